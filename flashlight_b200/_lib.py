@@ -27,7 +27,7 @@ E_TIMEOUT = -7
 SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP, SCORE_BIAS = 0, 1, 2, 3
 MASK_NONE, MASK_CAUSAL, MASK_SLIDING, MASK_PREFIX, MASK_DOCUMENT = 0, 1, 2, 3, 4
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 NOALLOC_SCRATCH_BYTES = 1 << 20
 
 
@@ -65,6 +65,9 @@ class AttnParams(C.Structure):
         ("status", C.c_void_p),
         ("lse", C.c_void_p),
         ("lse_stride", C.c_int64 * 2),
+        ("wait_limit_us", C.c_uint32),
+        ("status_host", C.c_void_p),
+        ("alibi_head0", C.c_int32),
     ]
 
 
@@ -76,6 +79,7 @@ EXPORTS = (
     "flb200_build_block_map",
     "flb200_attn_fwd",
     "flb200_attn_fwd_noalloc",
+    "flb200_selftest_wait_timeout",
     "flb200_decode_status",
     "flb200_launch_count",
 )
@@ -108,6 +112,8 @@ def load() -> C.CDLL:
     lib.flb200_attn_fwd.argtypes = [P, C.c_void_p]
     lib.flb200_attn_fwd_noalloc.restype = C.c_int
     lib.flb200_attn_fwd_noalloc.argtypes = [P, C.c_void_p]
+    lib.flb200_selftest_wait_timeout.restype = C.c_int
+    lib.flb200_selftest_wait_timeout.argtypes = [P, C.c_void_p]
     lib.flb200_decode_status.restype = C.c_int
     lib.flb200_decode_status.argtypes = [C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.flb200_launch_count.restype = C.c_uint64

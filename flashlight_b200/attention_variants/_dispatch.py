@@ -67,7 +67,7 @@ def _run_host_pipelined(query, key, value, device, args_for, n_chunks: int) -> t
 
 def run(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, scale: float,
         enable_gqa: bool = False, gqa_5d: bool = False,
-        score_mod: int = _lib.SCORE_NONE, alibi_heads: int = 0, softcap: float = 0.0,
+        score_mod: int = _lib.SCORE_NONE, alibi_heads: int = 0, alibi_head0: int = 0, softcap: float = 0.0,
         mask: int = _lib.MASK_NONE, causal: bool = False, window: int = 0,
         prefix_len: Optional[torch.Tensor] = None, prefix_scalar: int = 0,
         document_id: Optional[torch.Tensor] = None,
@@ -99,7 +99,8 @@ def run(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, scale: f
         pl_dev, doc_dev = _dev(prefix_len, device), _dev(document_id, device)
 
         def args_for(n0, n1):
-            return (float(scale), int(score_mod), int(alibi_heads), float(softcap), int(mask), bool(causal),
+            return (float(scale), int(score_mod), int(alibi_heads), int(alibi_head0), float(softcap), int(mask),
+                    bool(causal),
                     int(window), None if pl_dev is None else pl_dev[n0:n1], int(prefix_scalar),
                     None if doc_dev is None else doc_dev[n0:n1], None, None, int(bias_inner),
                     bool(diff), float(diff_lambda), bool(diff_rms_norm), float(diff_rms_eps), False)
@@ -109,7 +110,7 @@ def run(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, scale: f
             out = out.view(out.size(0), Hkv, Hq // Hkv, out.size(2), out.size(3))
         return out
     q, k, v = _dev(query, device), _dev(key, device), _dev(value, device)
-    out = attn_fwd(q, k, v, float(scale), int(score_mod), int(alibi_heads), float(softcap),
+    out = attn_fwd(q, k, v, float(scale), int(score_mod), int(alibi_heads), int(alibi_head0), float(softcap),
                    int(mask), bool(causal), int(window), _dev(prefix_len, device),
                    int(prefix_scalar), _dev(document_id, device), b0, b1, int(bias_inner),
                    bool(diff), float(diff_lambda), bool(diff_rms_norm), float(diff_rms_eps),

@@ -20,12 +20,17 @@ class AlibiScoreMod:
 
     kind = "alibi"
 
-    def __init__(self, nheads: int, device='cuda'):
+    def __init__(self, nheads: int, device='cuda', head_offset: int = 0, head_count=None):
         self.nheads = int(nheads)
         self.device = device
+        # a slice [head_offset, head_offset + head_count) of the heads, for callers that split the
+        # heads of one model over several calls (or GPUs); the default is all of them
+        self.head_offset = int(head_offset)
+        self.head_count = self.nheads if head_count is None else int(head_count)
 
     def __call__(self, q_len, kv_len):
-        return alibi_bias(self.nheads, q_len, kv_len, device=self.device)
+        bias = alibi_bias(self.nheads, q_len, kv_len, device=self.device)
+        return bias[self.head_offset:self.head_offset + self.head_count]
 
 
 def generate_alibi_bias_pytorch(nheads):
@@ -50,6 +55,10 @@ def attention_pytorch_alibi(
         raise NotImplementedError(
             "score_mod must be built by generate_alibi_bias_pytorch(); arbitrary callables "
             "cannot run inside the fused kernel and there is no fallback")
+    if score_mod.head_count != query.size(1):
+        # the reference adds a [nheads, L, S] bias to [N, Hq, L, S] scores (alibi.py:27-29): any
+        # other head count fails to broadcast there
+        raise ValueError(f"ALiBi bias built for {score_mod.head_count} heads, query has {query.size(1)}")
     return run(query, key, value, scale=default_scale(query, scale), enable_gqa=enable_gqa,
-               gqa_5d=True, score_mod=_lib.SCORE_ALIBI, alibi_heads=score_mod.nheads,
+               gqa_5d=True, score_mod=_lib.SCORE_ALIBI, alibi_heads=score_mod.nheads, alibi_head0=score_mod.head_offset,
                mask=_lib.MASK_CAUSAL if is_causal else _lib.MASK_NONE)

@@ -35,10 +35,21 @@
 
 namespace flb {
 
-template <int E_, int EV_, int SCORE_, int MASK_, bool DIFF_>
+template <int E_, int EV_, int SCORE_, int MASK_, bool DIFF_, int STAGES_ = 2>
 struct AttnCfg {
   static constexpr int E = E_, EV = EV_, SCORE = SCORE_, MASK = MASK_;
   static constexpr bool DIFF = DIFF_;
+  // Query tiles per CTA.  Two: 512 threads, all of tensor memory, one CTA per SM, the stages share
+  // every K/V tile.  One: 256 threads, half of tensor memory and of shared memory, two CTAs per
+  // SM that run independently, so one CTA's set-up and epilogue hide behind the other's tiles
+  // (short work items: sliding window, document mask, short sequences).
+  static constexpr int STAGES = STAGES_;
+  static_assert(STAGES == 2 || (STAGES == 1 && !DIFF_), "one or two query tiles per CTA");
+  static constexpr int THREADS = STAGES == 2 ? 512 : 256;
+  static constexpr int W_SOFTMAX_END = 4 * STAGES;                 // softmax warps [0, 4 * STAGES)
+  static constexpr int W_EPI = STAGES == 2 ? 8 : 0;                // epilogue warps (one-stage: the softmax warps)
+  static constexpr int W_MMA = STAGES == 2 ? 12 : 4;
+  static constexpr int W_TMA = W_MMA + 1;
   // Differential attention subtracts two nearly equal softmax averages and then normalises the
   // result to unit RMS, which amplifies the rounding of P to bf16 to about the size of the
   // tolerance.  There P is written as two bf16 terms (hi + lo) and the PV product runs on both.
@@ -50,7 +61,10 @@ struct AttnCfg {
   // Let the PV product start on the first 64 keys of P while the softmax warps still work on the
   // other 64.  It pays where the softmax of a tile is long (softcap: two transcendentals per
   // score); elsewhere the extra hand-off costs more than the overlap brings.
-  static constexpr bool EARLY_PV = SCORE_ == SCORE_SOFTCAP;
+#ifndef FLB_SOFTCAP_EARLY_PV
+#define FLB_SOFTCAP_EARLY_PV 1
+#endif
+  static constexpr bool EARLY_PV = FLB_SOFTCAP_EARLY_PV && SCORE_ == SCORE_SOFTCAP;
   static constexpr int KBOX = E >= 64 ? 64 : E;     // elements per swizzled row of a Q/K box
   static constexpr int VBOX = EV >= 64 ? 64 : EV;   // elements per swizzled row of a V box
   static constexpr int NKB = E / KBOX, NVB = EV / VBOX;
@@ -61,16 +75,22 @@ struct AttnCfg {
   static constexpr int K_BYTES = K_HEAD_BYTES * (DIFF ? 2 : 1);  // diff: two heads side by side
   static constexpr int V_BYTES = 128 * EV * 2;
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
-  static constexpr int NSTAGE_FIT = (224 * 1024 - 2 * Q_BYTES) / SLOT_BYTES;
+  static constexpr int SMEM_BUDGET = STAGES == 2 ? 224 * 1024 : 110 * 1024;
+  static constexpr int NSTAGE_FIT = (SMEM_BUDGET - STAGES * Q_BYTES) / SLOT_BYTES;
   static constexpr int NSTAGE = NSTAGE_FIT > 8 ? 8 : NSTAGE_FIT;
   static constexpr int AUX_BYTES = 2048;
-  static constexpr int SMEM_USED = 1024 + 2 * Q_BYTES + NSTAGE * SLOT_BYTES + AUX_BYTES;
-  // At least half the SM's shared memory, so two CTAs never share an SM (each wants all of TMEM).
-  static constexpr int SMEM_BYTES = SMEM_USED < 120 * 1024 ? 120 * 1024 : SMEM_USED;
+  static constexpr int SMEM_USED = 1024 + STAGES * Q_BYTES + NSTAGE * SLOT_BYTES + AUX_BYTES;
+  // Shared memory also bounds how many CTAs share an SM, and with it their tensor-memory demand
+  // (an allocation that does not fit would wait for a neighbour to leave): two-stage CTAs take
+  // more than half of it (512 columns each), one-stage CTAs more than a third (256 columns each).
+  static constexpr int SMEM_FLOOR = STAGES == 2 ? 120 * 1024 : 80 * 1024;
+  static constexpr int SMEM_BYTES = SMEM_USED < SMEM_FLOOR ? SMEM_FLOOR : SMEM_USED;
+  static_assert(STAGES == 2 || SMEM_BYTES <= 113 * 1024, "two one-stage CTAs must fit one SM");
   static constexpr uint32_t SWZ_K = KBOX == 64 ? kSwz128 : (KBOX == 32 ? kSwz64 : kSwz32);
   static constexpr uint32_t SWZ_V = VBOX == 64 ? kSwz128 : (VBOX == 32 ? kSwz64 : kSwz32);
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int COL_S0 = 0, COL_S1 = 128, COL_O0 = 256, COL_O1 = 256 + EV;
+  static constexpr int TMEM_COLS = STAGES == 2 ? 512 : 256;
+  static constexpr int COL_S0 = 0, COL_S1 = 128;
+  static constexpr int COL_O0 = STAGES == 2 ? 256 : 128, COL_O1 = 256 + EV;
   // With value heads of 64 or less the accumulators leave 128 columns free: P gets columns of
   // its own instead of overwriting S.  The next QK product of a stage can then start as soon as
   // the softmax warps have read S, without waiting for P and the PV product: the softmax never
@@ -86,7 +106,8 @@ struct AttnCfg {
 #endif
   static constexpr bool SPECULATE = FLB_SPECULATE && !DIFF_ && !EARLY_PV && MASK_ != MASK_DOCUMENT &&
                                     (FLB_SPECULATE_SEP || !SEP_P);
-  static constexpr int COL_P0 = 384, COL_P1 = 448;
+  static constexpr int COL_P0 = STAGES == 2 ? 384 : 128 + EV, COL_P1 = 448;
+  static_assert(!SEP_P || COL_P0 + 64 <= TMEM_COLS, "P columns do not fit");
   static_assert(E % 16 == 0 && EV % 16 == 0, "head dims must be multiples of 16");
   static_assert(E <= 128 && EV <= 128, "head dims above 128 are not supported");
   static_assert(NSTAGE >= 2, "ring too small");
@@ -165,51 +186,26 @@ template <class C>
 struct Smem {
   uint8_t* base;
   FLB_DEV uint8_t* q(int s) const { return base + s * C::Q_BYTES; }
-  FLB_DEV uint8_t* slot(int i) const { return base + 2 * C::Q_BYTES + i * C::SLOT_BYTES; }
-  FLB_DEV uint8_t* aux() const { return base + 2 * C::Q_BYTES + C::NSTAGE * C::SLOT_BYTES; }
+  FLB_DEV uint8_t* slot(int i) const { return base + C::STAGES * C::Q_BYTES + i * C::SLOT_BYTES; }
+  FLB_DEV uint8_t* aux() const { return base + C::STAGES * C::Q_BYTES + C::NSTAGE * C::SLOT_BYTES; }
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
   FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }
-  FLB_DEV volatile int* abort_flag() const { return reinterpret_cast<volatile int*>(aux() + 260); }
-  FLB_DEV int* fail_bar() const { return reinterpret_cast<int*>(aux() + 264); }
+  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
   FLB_DEV float* scale(int s) const { return reinterpret_cast<float*>(aux() + 512) + s * 128; }
 };
 
-#ifdef FLB_TRACE
-struct Tracer {
-  unsigned long long* slot;
-  int n;
-  FLB_DEV Tracer(const KernelParams& p, int role, bool on) : slot(nullptr), n(0) {
-    if (on && p.trace && static_cast<int>(blockIdx.x) < p.trace_ctas)
-      slot = p.trace + (static_cast<size_t>(blockIdx.x) * 8 + role) * 128;
-  }
-  FLB_DEV void mark(int tag) {
-    if (slot && n < 128) slot[n++] = (static_cast<unsigned long long>(tag) << 48) | (globaltimer_ns() & 0xffffffffffffull);
-  }
-  // SM cycle counter instead of the nanosecond timer: a pair of each gives the SM clock
-  FLB_DEV void mark_cycles(int tag) {
-    if (slot && n < 128) slot[n++] = (static_cast<unsigned long long>(tag) << 48) | (static_cast<unsigned long long>(clock64()) & 0xffffffffffffull);
-  }
-};
-#else
-struct Tracer {
-  FLB_DEV Tracer(const KernelParams&, int, bool) {}
-  FLB_DEV void mark(int) {}
-  FLB_DEV void mark_cycles(int) {}
-};
-#endif
-
 #define FLB_WAIT_RET(sm, id, parity, ret)                         \
   do {                                                            \
-    if (!mbar_wait((sm).bar(id), (parity), (sm).abort_flag())) {  \
-      atomicCAS((sm).fail_bar(), -1, (id));                       \
+    if (!mbar_wait((sm).bar(id), (parity), (sm).ctl())) {         \
+      atomicCAS(&(sm).ctl()->fail_bar, -1, (id));                 \
       return ret;                                                 \
     }                                                             \
   } while (0)
 
 #define FLB_WAIT(sm, id, parity)                                  \
   do {                                                            \
-    if (!mbar_wait((sm).bar(id), (parity), (sm).abort_flag())) {  \
-      atomicCAS((sm).fail_bar(), -1, (id));                       \
+    if (!mbar_wait((sm).bar(id), (parity), (sm).ctl())) {         \
+      atomicCAS(&(sm).ctl()->fail_bar, -1, (id));                 \
       return;                                                     \
     }                                                             \
   } while (0)
@@ -221,11 +217,11 @@ template <class C>
 FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensorMap* tmK,
                        const CUtensorMap* tmV, const KernelParams& p, int n, int h,
                        const int (&r0)[2], const TileRange (&rg)[2], int lo, int hi) {
-  Tracer tr(p, 5, true);
-  tr.mark(1);
+  // wait self-test: nothing is loaded, so the first wait of every other role runs into its limit
+  if (p.withhold_loads) return;
   const int kvh = h / p.G;
 #pragma unroll
-  for (int s = 0; s < 2; ++s) {
+  for (int s = 0; s < C::STAGES; ++s) {
     if (rg[s].hi > rg[s].lo) {
       const int qh = C::DIFF ? h + s * p.diff_heads : h;
       mbar_arrive_expect_tx(sm.bar(BAR_Q_FULL + s), C::Q_BYTES);
@@ -243,7 +239,6 @@ FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensor
       const int slot = seq % C::NSTAGE;
       const uint32_t ph = (seq / C::NSTAGE) & 1;
       FLB_WAIT(sm, BAR_KV_EMPTY + slot, ph ^ 1);
-      tr.mark(2);
       mbar_arrive_expect_tx(sm.bar(BAR_KV_FULL + slot), C::K_BYTES);
       const uint32_t dst = smem_u32(sm.slot(slot));
 #pragma unroll
@@ -282,8 +277,6 @@ template <class C>
 FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                       const TileRange (&rg)[2], int lo, int hi) {
   const uint32_t leader = elect_one() ? 1u : 0u;  // the lane that issues; all lanes run the loop
-  Tracer tr(p, 4, leader != 0);
-  tr.mark(1);
   constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, 0);
   constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
   const uint32_t tS[2] = {tmem + C::COL_S0, tmem + C::COL_S1};
@@ -317,7 +310,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
     if (have_v) FLB_WAIT(sm, BAR_KV_FULL + vslot, (vseq / C::NSTAGE) & 1);
     if (have_k) FLB_WAIT(sm, BAR_KV_FULL + kslot, (kseq / C::NSTAGE) & 1);
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < C::STAGES; ++s) {
       // With P in columns of its own the scores of the next tile go first (they only wait for S to
       // be read), otherwise the PV product that frees the S tile.
 #pragma unroll
@@ -333,7 +326,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
             } else {
               FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
             }
-            tr.mark(10 + s);
             tc_fence_after();
             if (it > 0) umma_ts_c<1>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
             else umma_ts_c<0>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
@@ -348,7 +340,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
             }
             if constexpr (C::EARLY_PV) {
               FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
-              tr.mark(12 + s);
               tc_fence_after();
             }
 #pragma unroll
@@ -378,7 +369,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                 tc_fence_after();
               }
             }
-            tr.mark(14 + s);
             const uint32_t ks_lo = k_lo + (C::DIFF ? s * (C::K_HEAD_BYTES >> 4) : 0);
             umma_ss_c<0>(leader, tS[s], q_lo[s], ks_lo, k_hi, idesc_qk);
 #pragma unroll
@@ -408,6 +398,8 @@ FLB_DEV uint32_t f2u(float f) { return __float_as_uint(f); }
 constexpr float kLazyRescaleLog2 = 8.0f;
 // a tile tried with the running maximum stands when each of its row sums is at most this
 constexpr float kSpeculateSumLimit = 1024.0f;
+// largest (score / cap)^2 for which the softcap's tanh is taken from its odd polynomial
+constexpr float kSoftcapPolyLimit = 0.09f;
 
 // 2^x for a pair of non-positive-ish arguments on the FMA pipe, to take load off the
 // transcendental unit (16 ex2 per clock and SM would otherwise bound the kernel).
@@ -435,6 +427,12 @@ FLB_DEV float2 exp2_poly2(float2 x) {
 #define FLB_REGS_SOFTMAX 192
 #define FLB_REGS_EPILOGUE 64
 #define FLB_REGS_ISSUE 64
+#endif
+// one query tile per CTA: 256 threads start with 128 registers each (two CTAs per SM); four
+// softmax warps and the warpgroup around the two issuing warps: 128 * softmax + 128 * issue <= 32768
+#ifndef FLB_REGS_SOFTMAX1
+#define FLB_REGS_SOFTMAX1 200
+#define FLB_REGS_ISSUE1 56
 #endif
 
 // Of every FLB_POLY_PERIOD column pairs, FLB_POLY_COUNT go through exp2_poly2, the rest through
@@ -473,7 +471,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
 
   float slope2 = 0.f;
   if constexpr (C::SCORE == SCORE_ALIBI) {
-    const int qh = h;  // the slope follows the query head
+    const int qh = h + p.alibi_head0;  // the slope follows the query head
     slope2 = exp2f(static_cast<float>(qh + 1) * p.alibi_log2_slope_step) * kLog2e;
   }
   const __nv_bfloat16* brow[2] = {nullptr, nullptr};
@@ -507,8 +505,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     }
   }
 
-  Tracer tr(p, s, row == 0);
-  tr.mark(1);
   float m = -CUDART_INF_F;  // running maximum (in the domain of x below)
   float l = 0.f;            // running sum of exp2
 
@@ -529,7 +525,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
         }
     }
     FLB_WAIT(sm, BAR_S_FULL + s, it & 1);
-    tr.mark(2);
     tc_fence_after();
     uint32_t v[128];
     float m_new = m, m_use = 0.f, sc = 1.0f;
@@ -550,9 +545,30 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
         v[c] = f2u(fmaf(u2f(v[c]), p.scale_log2, fmaf(slope2, static_cast<float>(c), base)));
     } else if constexpr (C::SCORE == SCORE_SOFTCAP) {
       const float inv = p.scale / p.softcap;
-      // the cap and log2(e) join the exponent FMA below (kmul, mdom): tanh in, tanh out here
+      // the cap and log2(e) join the exponent FMA below (kmul, mdom): tanh in, tanh out here.
+      // A softcap is chosen well above the typical score, so y = score / cap is small and
+      // tanh(y) = y (1 + y^2 (-1/3 + 2/15 y^2)) holds to 1.2e-5 for |y| <= 0.3: packed FMA-pipe
+      // work instead of one more transcendental per score on the unit the exponentials already
+      // saturate.  A warp whose tile holds a larger |y| (small caps) redoes it with tanh.approx.
+      const float2 inv2 = make_float2(inv, inv), one2 = make_float2(1.f, 1.f);
+      const float2 c3 = make_float2(-1.f / 3.f, -1.f / 3.f), c5 = make_float2(2.f / 15.f, 2.f / 15.f);
+      float y2m = 0.f;
 #pragma unroll
-      for (int c = 0; c < 128; ++c) v[c] = f2u(tanh_approx(u2f(v[c]) * inv));
+      for (int c = 0; c < 128; c += 2) {
+        float2 y = __fmul2_rn(make_float2(u2f(v[c]), u2f(v[c + 1])), inv2);
+        const float2 y2 = __fmul2_rn(y, y);
+        y2m = max3(y2m, y2.x, y2.y);
+        float2 a = __ffma2_rn(y2, c5, c3);
+        a = __ffma2_rn(a, y2, one2);
+        y = __fmul2_rn(y, a);
+        v[c] = f2u(y.x);
+        v[c + 1] = f2u(y.y);
+      }
+      if (!__all_sync(0xffffffffu, y2m <= kSoftcapPolyLimit)) {
+        tmem_ld128_sync(tS, v);
+#pragma unroll
+        for (int c = 0; c < 128; ++c) v[c] = f2u(tanh_approx(u2f(v[c]) * inv));
+      }
     } else if constexpr (C::SCORE == SCORE_BIAS) {
       const bool ragged = j0 + kTileN > p.S;
       // s * scale + b0 + b1: the scale rides on the first bias as one FMA per score
@@ -656,7 +672,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     if constexpr (C::SPECULATE) {
       if (it > 0 && __all_sync(0xffffffffu, m != -CUDART_INF_F)) {
         fetch_scores(std::true_type{});
-        tr.mark(3);
         const float mk = m * mdom;
         const float2 kmul2 = make_float2(kmul, kmul), nmk2 = make_float2(-mk, -mk);
         [[maybe_unused]] float2 slope22, base2, scale2;
@@ -716,7 +731,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     for (int pass = 0; pass < 2; ++pass) {
     fetch_scores(std::false_type{});
     if (pass == 1) break;
-    tr.mark(3);
 
     // ---- row maximum (four independent chains) ----
     float mxs[4];
@@ -764,7 +778,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     }
     l *= sc;
     m = m_new;
-    tr.mark(5);
 
     // ---- probabilities, row sum, bf16 P back into TMEM ----
     const float mk = m_use * mdom;
@@ -806,21 +819,21 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     }
     l += (suma.x + suma.y) + (sumb.x + sumb.y);
     }  // !done
-    tr.mark(6);
     tmem_wait_st();
     tc_fence_before();
     mbar_arrive(sm.bar(BAR_P_FULL + s));
-    tr.mark(4);
   }
 
-  // final row sum for the epilogue
-  sscale[row] = l;
+  // Final row sum for the epilogue.  A row that saw no key (every score masked or -inf) still has
+  // m = -inf; its sum may hold the tiny terms of clamped polynomial exponentials, so the running
+  // maximum decides: such a row gets sum 0, which the epilogue turns into a row of zeros.
+  const bool no_key = m == -CUDART_INF_F;
+  sscale[row] = no_key ? 0.f : l;
   mbar_arrive(sm.bar(BAR_SCALE_FULL + s));
   if constexpr (!C::DIFF) {
     // log-sum-exp of the row: m and log2(l) are in log2 units of the modified scores
     if (p.lse != nullptr && i < p.L) {
-      const float m_fin = m == -CUDART_INF_F ? 0.f : m;
-      const float lse2 = l > 0.f ? fmaf(m_fin, mdom, log2f(l)) : -CUDART_INF_F;
+      const float lse2 = (no_key || !(l > 0.f)) ? -CUDART_INF_F : fmaf(m, mdom, log2f(l));
       p.lse[n * p.lse_sn + h * p.lse_sh + i] = lse2 * 0.6931471805599453f;
     }
   }
@@ -836,8 +849,6 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
   const int row = threadIdx.x & 127;
   const uint32_t lane_base = static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32u;
   const uint32_t tO[2] = {tmem + C::COL_O0 + (lane_base << 16), tmem + C::COL_O1 + (lane_base << 16)};
-  Tracer tr(p, 2, row == 0);
-  tr.mark(2);
   // The output tile goes to global memory as one TMA store per 64-column box: every thread puts
   // its row into shared memory (the stage's Q tile is dead by then) in the swizzled layout the
   // tensor map expects, and one thread issues the store once all 128 rows are in place.  Row-wise
@@ -863,13 +874,12 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
   };
   if constexpr (!C::DIFF) {
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < C::STAGES; ++s) {
       const int ns = rg[s].hi - rg[s].lo;
       if (ns <= 0) continue;
       FLB_WAIT(sm, BAR_SCALE_FULL + s, 0);
       const float l = sm.scale(s)[row];
       FLB_WAIT(sm, BAR_PV_DONE + s, (ns - 1) & 1);
-      tr.mark(3);
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       uint8_t* tile = sm.q(s);  // E == EV here: the Q tile holds exactly one output tile
@@ -948,7 +958,7 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
 // kernel
 // ------------------------------------------------------------------------------------------
 template <class C>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(C::THREADS, C::STAGES == 2 ? 1 : 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                 const __grid_constant__ KernelParams p) {
@@ -957,8 +967,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                         ~static_cast<uintptr_t>(1023))};
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  Tracer ktr(p, 6, threadIdx.x == 0);
-  ktr.mark(1);
 
   // Order of the work items over blockIdx.x (thread blocks start in that order): the (batch, head)
   // axis is cut into sections whose K/V fit in L2 together; inside a section the query blocks run
@@ -974,7 +982,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int bh = bh0 + wi % width;
   const int n = bh / p.H, h = bh % p.H;
   int r0[2];
-  if constexpr (C::DIFF) {
+  if constexpr (C::DIFF || C::STAGES == 1) {
     r0[0] = r0[1] = qb * kTileM;
   } else {
     r0[0] = qb * 2 * kTileM;
@@ -982,22 +990,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
   TileRange rg[2];
   rg[0] = tile_range<C::MASK>(p, n, r0[0]);
-  rg[1] = tile_range<C::MASK>(p, n, r0[1]);
+  rg[1] = C::STAGES == 2 ? tile_range<C::MASK>(p, n, r0[1]) : TileRange{0, 0};
   int lo = 0x7fffffff, hi = 0;
 #pragma unroll
-  for (int s = 0; s < 2; ++s)
+  for (int s = 0; s < C::STAGES; ++s)
     if (rg[s].hi > rg[s].lo) {
       lo = min(lo, rg[s].lo);
       hi = max(hi, rg[s].hi);
     }
   if (hi == 0) lo = 0;
 
-  // Set-up, one block-wide barrier: the lanes of warp 0 initialise one mbarrier each while warp 1
-  // allocates tensor memory and the producer lane fetches the tensor maps.
+  // Set-up: the lanes of warp 0 initialise one mbarrier each while warp 1 allocates tensor memory
+  // and the producer lane fetches the tensor maps.  The producer warp needs only the mbarriers: it
+  // meets warp 0 on a barrier of their own and starts the first loads while the rest of the CTA
+  // still waits for the tensor-memory allocation.
   if (warp == 0) {
     if (lane == 0) {
-      *sm.abort_flag() = 0;
-      *sm.fail_bar() = -1;
+      sm.ctl()->abort = 0;
+      sm.ctl()->fail_bar = -1;
+      sm.ctl()->limit_us = p.wait_limit_us;
     }
     if (lane < BAR_COUNT) {
       const bool all_threads = (lane >= BAR_P_FULL && lane < BAR_PV_DONE) ||
@@ -1005,41 +1016,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(sm.bar(lane), all_threads ? 128 : 1);  // 128 arriving threads, or one commit / TMA
     }
     fence_mbar_init();
+    named_bar_sync(1, 64);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(sm.tmem_base()), C::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 13 && lane == 0) {
-    tma_prefetch_desc(&tmQ);
-    tma_prefetch_desc(&tmK);
-    tma_prefetch_desc(&tmV);
-    tma_prefetch_desc(&tmO);
+  uint32_t tmem = 0;
+  if (warp == C::W_TMA) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmO);
+    }
+    named_bar_sync(1, 64);
+  } else {
+    tc_fence_before();
+    named_bar_sync(2, C::THREADS - 32);
+    tc_fence_after();
+    tmem = *sm.tmem_base();
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *sm.tmem_base();
-  // A launch in which some CTA already gave up is not worth finishing: an epilogue thread (idle
-  // until the end) looks at the status word and raises the abort flag, which ends every role at
-  // its next long wait.  The look-up stays off the path to the first MMA.
-  if (threadIdx.x == 8 * 32 && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0)
-    *sm.abort_flag() = 1;
-  ktr.mark(2);
-  ktr.mark_cycles(20);
+  // A launch in which some CTA already gave up is not worth finishing: one thread of the MMA warp's
+  // group that has nothing else to do looks at the status word and raises the abort flag, which
+  // ends every role at its next long wait.  The look-up stays off the path to the first MMA.
+  if (threadIdx.x == (C::W_MMA + 2) * 32 && p.status != nullptr &&
+      *reinterpret_cast<volatile int*>(p.status) != 0)
+    sm.ctl()->abort = 1;
 
-  if (warp < 8) {
-    reg_inc<FLB_REGS_SOFTMAX>();
+  if (warp < C::W_SOFTMAX_END) {
+    reg_inc<C::STAGES == 2 ? FLB_REGS_SOFTMAX : FLB_REGS_SOFTMAX1>();
     const int s = warp >> 2;
     if (rg[s].hi > rg[s].lo) softmax_role<C>(sm, tmem, p, s, n, h, r0[s], rg[s]);
-  } else if (warp < 12) {
+    // one query tile per CTA: its softmax warps also write the result
+    if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, r0, rg, lo, hi);
+  } else if (C::STAGES == 2 && warp < 12) {
     reg_dec<FLB_REGS_EPILOGUE>();
     epilogue_role<C>(sm, tmem, &tmO, p, n, h, r0, rg, lo, hi);
   } else {
-    reg_dec<FLB_REGS_ISSUE>();
+    reg_dec<C::STAGES == 2 ? FLB_REGS_ISSUE : FLB_REGS_ISSUE1>();
     if (hi > lo) {
-      if (warp == 12) mma_role<C>(sm, tmem, p, rg, lo, hi);
-      if (warp == 13 && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, r0, rg, lo, hi);
+      if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi);
+      if (warp == C::W_TMA && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, r0, rg, lo, hi);
     }
     __syncwarp();
   }
@@ -1047,17 +1065,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // common exit: every role arrives here, also after a timed-out wait
   tc_fence_before();
   __syncthreads();
-  ktr.mark(3);
-  ktr.mark_cycles(30);
-  if (*sm.abort_flag()) {
+  if (sm.ctl()->abort) {
     // give loads that are still in flight time to land before shared memory and TMEM go away
     for (int k = 0; k < 64; ++k) __nanosleep(20000);
-    if (threadIdx.x == 0 && p.status)
-      atomicCAS(p.status, 0,
-                (kStatusTimeout << 24) | ((*sm.fail_bar() & 0xff) << 16) | (blockIdx.x & 0xffff));
+    if (threadIdx.x == 0 && p.status) {
+      const int word =
+          (kStatusTimeout << 24) | ((sm.ctl()->fail_bar & 0xff) << 16) | (blockIdx.x & 0xffff);
+      if (atomicCAS(p.status, 0, word) == 0 && p.status_host != nullptr) {
+        *reinterpret_cast<volatile int*>(p.status_host) = word;
+        __threadfence_system();
+      }
+    }
     __syncthreads();
   }
-  if (warp == 1) tmem_dealloc(tmem, C::TMEM_COLS);
+  if (warp == 1) tmem_dealloc(*sm.tmem_base(), C::TMEM_COLS);
 }
 
 }  // namespace flb

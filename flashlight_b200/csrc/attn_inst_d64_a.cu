@@ -1,10 +1,10 @@
 // head dim 64: plain and causal, with and without ALiBi / softcap
 #include "attn_launch_impl.cuh"
 namespace flb {
-FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_NONE, false)
-FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_CAUSAL, false)
-FLB_INSTANTIATE(64, 64, SCORE_ALIBI, MASK_NONE, false)
-FLB_INSTANTIATE(64, 64, SCORE_ALIBI, MASK_CAUSAL, false)
-FLB_INSTANTIATE(64, 64, SCORE_SOFTCAP, MASK_NONE, false)
-FLB_INSTANTIATE(64, 64, SCORE_SOFTCAP, MASK_CAUSAL, false)
+FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_NONE, false, 2)
+FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_CAUSAL, false, 2)
+FLB_INSTANTIATE(64, 64, SCORE_ALIBI, MASK_NONE, false, 2)
+FLB_INSTANTIATE(64, 64, SCORE_ALIBI, MASK_CAUSAL, false, 2)
+FLB_INSTANTIATE(64, 64, SCORE_SOFTCAP, MASK_NONE, false, 2)
+FLB_INSTANTIATE(64, 64, SCORE_SOFTCAP, MASK_CAUSAL, false, 2)
 }

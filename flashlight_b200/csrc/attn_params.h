@@ -35,7 +35,8 @@ struct KernelParams {
   // scores
   float scale;        // applied to q.k
   float scale_log2;   // scale * log2(e)
-  float alibi_log2_slope_step;  // -8 / n_heads: slope_h = 2^((h+1) * step)
+  float alibi_log2_slope_step;  // -8 / n_heads: slope_h = 2^((alibi_head0 + h + 1) * step)
+  int alibi_head0;
   float softcap;      // cap
   // additive biases (bf16), row pointer = base + b*sb + r*sr + h*sh + i*sl, keys contiguous
   const void* bias[2];
@@ -60,11 +61,9 @@ struct KernelParams {
   int nq_blocks;   // CTAs along the query axis
   int sec_bh;      // (batch, head) pairs per L2 section: their K/V together fit in L2
   int* status;     // device int32, 0 = ok; may be null
-  // Optional timeline for kernel tuning (only read by builds with FLB_TRACE defined):
-  // CTAs with blockIdx.x < trace_ctas write (tag << 48 | globaltimer ns) words into
-  // trace[blockIdx.x][role][slot], 8 roles x 128 slots per CTA.
-  unsigned long long* trace;
-  int trace_ctas;
+  int* status_host;  // pinned host int32 (device-accessible) that receives a copy; may be null
+  uint32_t wait_limit_us;  // limit of every device-side wait
+  int withhold_loads;      // wait self-test: the producer issues no loads
 };
 
 // status word layout: (code << 24) | (barrier id << 16) | (block index & 0xffff)

@@ -8,6 +8,7 @@
 
 #include "../../include/flb200_attn.h"
 #include "attn_launch.h"
+#include "ptx.cuh"
 #include "block_map.cuh"
 #include "tmap.h"
 
@@ -16,10 +17,6 @@ namespace {
 using namespace flb;
 
 std::atomic<uint64_t> g_launches{0};
-#ifdef FLB_TRACE
-unsigned long long* g_trace = nullptr;
-int g_trace_ctas = 0;
-#endif
 
 // Scratch for flb200_attn_fwd_noalloc: lives in the library image of every device that loads it.
 // In host code `g_noalloc_scratch` is only a stand-in for the symbol; the device address comes
@@ -67,16 +64,14 @@ MapLayout map_layout(const flb200_attn_params* p) {
   return m;
 }
 
-bool kernel_exists(int E, int EV, int score, int mask, int diff) {
-  if (diff) {
-    return ((E == 64 && EV == 128) || (E == 32 && EV == 64)) && score == SCORE_NONE &&
-           (mask == MASK_NONE || mask == MASK_CAUSAL);
-  }
-  if (E != EV) return false;
-  if (E == 32)
+// Head dims a kernel is built for.  Narrower heads run on the next wider kernel: the tensor maps
+// carry the true widths, so the loads fill the missing feature columns with zeros (they add nothing
+// to q.k, and the value columns beyond Ev are clipped by the output store).
+bool kernel_built(int D, int score, int mask) {
+  if (D == 32)
     return (score == SCORE_NONE && (mask == MASK_NONE || mask == MASK_CAUSAL)) ||
            (score == SCORE_BIAS && mask == MASK_NONE);
-  if (E != 64 && E != 128) return false;
+  if (D != 64 && D != 128) return false;
   switch (score) {
     case SCORE_NONE:
       return true;
@@ -87,6 +82,22 @@ bool kernel_exists(int E, int EV, int score, int mask, int diff) {
       return mask == MASK_NONE;
   }
   return false;
+}
+
+// Width of the kernel that serves (E, Ev): plain variants use one width for q/k and v; the
+// differential kernels come as (q/k width, v width) = (32, 64) and (64, 128), returned as the
+// q/k width.  0 = no kernel.
+int kernel_width(int E, int EV, int score, int mask, int diff) {
+  if (diff) {
+    if (score != SCORE_NONE || (mask != MASK_NONE && mask != MASK_CAUSAL)) return 0;
+    if (E <= 32 && EV <= 64) return 32;
+    if (E <= 64 && EV <= 128) return 64;
+    return 0;
+  }
+  const int need = E > EV ? E : EV;
+  for (int D : {32, 64, 128})
+    if (D >= need && kernel_built(D, score, mask)) return D;
+  return 0;
 }
 
 int validate(const flb200_attn_params* p) {
@@ -102,13 +113,18 @@ int validate(const flb200_attn_params* p) {
   if (p->lse) {
     if (p->diff) return FLB200_E_UNSUPPORTED;  // two softmaxes per output head: no single log-sum-exp
     if (reinterpret_cast<uintptr_t>(p->lse) & 3u) return FLB200_E_MISALIGNED;
+    // rows of L floats that do not overlap
+    if ((p->Hq > 1 && p->lse_stride[1] < p->L) || (p->N > 1 && p->lse_stride[0] < p->L))
+      return FLB200_E_BAD_ARG;
+    if (p->lse_stride[0] < 0 || p->lse_stride[1] < 0) return FLB200_E_BAD_ARG;
   }
   if (p->diff) {
     if (p->Hq != p->Hkv || p->Hq % 2 != 0) return FLB200_E_BAD_ARG;
     if (!std::isfinite(p->diff_lambda)) return FLB200_E_BAD_ARG;
     if (p->diff_rms_norm && !(p->diff_rms_eps >= 0.f)) return FLB200_E_BAD_ARG;
   }
-  if (p->score_mod == FLB200_SCORE_ALIBI && p->alibi_heads <= 0) return FLB200_E_BAD_ARG;
+  if (p->score_mod == FLB200_SCORE_ALIBI && (p->alibi_heads <= 0 || p->alibi_head0 < 0))
+    return FLB200_E_BAD_ARG;
   if (p->score_mod == FLB200_SCORE_SOFTCAP && !(p->softcap > 0.f && std::isfinite(p->softcap)))
     return FLB200_E_BAD_ARG;
   if (p->score_mod == FLB200_SCORE_BIAS) {
@@ -118,7 +134,13 @@ int validate(const flb200_attn_params* p) {
   if (p->mask == FLB200_MASK_SLIDING && p->window < 0) return FLB200_E_BAD_ARG;
   if (p->mask == FLB200_MASK_PREFIX && !p->prefix_len && p->prefix_scalar < 0)
     return FLB200_E_BAD_ARG;
-  if (p->mask == FLB200_MASK_DOCUMENT && !p->document_id) return FLB200_E_BAD_ARG;
+  if (p->mask == FLB200_MASK_DOCUMENT) {
+    if (!p->document_id) return FLB200_E_BAD_ARG;
+    if (reinterpret_cast<uintptr_t>(p->document_id) & 7u) return FLB200_E_MISALIGNED;
+    // one row of L ids per sequence, or one shared row (stride 0)
+    if (p->N > 1 && p->doc_stride_n != 0 && p->doc_stride_n < p->L) return FLB200_E_BAD_ARG;
+    if (p->N > 65535) return FLB200_E_UNSUPPORTED;  // the map builder puts the batch on gridDim.y
+  }
   // these masks are defined on square score matrices (sliding_window.py:27, prefix_lm.py:37-38,
   // document_mask.py:25-27 index keys and queries with the same ids)
   if ((p->mask == FLB200_MASK_SLIDING || p->mask == FLB200_MASK_PREFIX ||
@@ -126,7 +148,7 @@ int validate(const flb200_attn_params* p) {
       p->L != p->S)
     return FLB200_E_BAD_ARG;
 
-  if (!kernel_exists(p->E, p->Ev, p->score_mod, p->mask, p->diff)) return FLB200_E_UNSUPPORTED;
+  if (!kernel_width(p->E, p->Ev, p->score_mod, p->mask, p->diff)) return FLB200_E_UNSUPPORTED;
   if (p->L > (1 << 24) || p->S > (1 << 24)) return FLB200_E_UNSUPPORTED;
   {
     const int H = p->diff ? p->Hq / 2 : p->Hq;
@@ -162,6 +184,22 @@ int validate(const flb200_attn_params* p) {
   return FLB200_OK;
 }
 
+// Query tiles per CTA (see AttnCfg::STAGES).  Two stages share every K/V tile and win on long,
+// regular work items (no mask, causal, prefix-LM, sliding window).  One stage per CTA, two CTAs
+// per SM, wins where items are short or ragged, because one CTA's set-up and epilogue overlap the
+// other's tiles: document masks, additive biases (Evoformer rows), and launches too small to give
+// every SM two-stage work.  FLB200_STAGES=1|2 overrides the choice for tuning.
+int pick_stages(const flb200_attn_params* p) {
+  if (p->diff) return 2;
+  if (const char* e = std::getenv("FLB200_STAGES")) {
+    const int v = std::atoi(e);
+    if (v == 1 || v == 2) return v;
+  }
+  if (p->mask == FLB200_MASK_DOCUMENT || p->score_mod == FLB200_SCORE_BIAS) return 1;
+  const long long ctas2 = static_cast<long long>((p->L + 2 * kTileM - 1) / (2 * kTileM)) * p->N * p->Hq;
+  return ctas2 < 2 * 148 ? 1 : 2;
+}
+
 int check_arch() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return FLB200_E_LAUNCH;
@@ -184,16 +222,18 @@ int build_block_map(const flb200_attn_params* p, cudaStream_t stream) {
   dim3 grid2((p->L + 255) / 256, p->N);
   doc_runs_kernel<<<grid2, 256, 0, stream>>>(reinterpret_cast<const long long*>(p->document_id),
                                              p->doc_stride_n, p->L, sorted, runs);
+  if (cudaGetLastError() != cudaSuccess) return FLB200_E_LAUNCH;
   g_launches.fetch_add(2, std::memory_order_relaxed);
-  return cudaGetLastError() == cudaSuccess ? FLB200_OK : FLB200_E_LAUNCH;
+  return FLB200_OK;
 }
 
-template <int E, int EV, bool DIFF>
+template <int E, int EV, bool DIFF, int STAGES>
 cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUtensorMap& b,
                           const CUtensorMap& c, const CUtensorMap& o, const KernelParams& kp,
                           int grid, cudaStream_t st) {
-#define FLB_CASE(SC, MK)                                                   \
-  if (score == SC && mask == MK) return launch_attn<E, EV, SC, MK, DIFF>(a, b, c, o, kp, grid, st);
+#define FLB_CASE(SC, MK)          \
+  if (score == SC && mask == MK)  \
+    return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, kp, grid, st);
   if constexpr (DIFF) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
@@ -254,7 +294,24 @@ int flb200_build_block_map(const flb200_attn_params* p, void* cuda_stream) {
   return build_block_map(p, static_cast<cudaStream_t>(cuda_stream));
 }
 
+namespace {
+int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_loads);
+}
+
 int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream) {
+  return attn_fwd_impl(p, cuda_stream, false);
+}
+
+int flb200_selftest_wait_timeout(const flb200_attn_params* p, void* cuda_stream) {
+  if (!p || p->struct_size != sizeof(flb200_attn_params)) return FLB200_E_BAD_ARG;
+  if (!p->status) return FLB200_E_BAD_ARG;
+  flb200_attn_params q = *p;
+  if (q.wait_limit_us == 0) q.wait_limit_us = 1000;
+  return attn_fwd_impl(&q, cuda_stream, true);
+}
+
+namespace {
+int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_loads) {
   const int v = validate(p);
   if (v != FLB200_OK) return v;
   const int a = check_arch();
@@ -278,6 +335,7 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream) {
   kp.scale = p->scale;
   kp.scale_log2 = p->scale * 1.4426950408889634f;
   kp.alibi_log2_slope_step = p->score_mod == FLB200_SCORE_ALIBI ? -8.0f / p->alibi_heads : 0.f;
+  kp.alibi_head0 = p->alibi_head0;
   kp.softcap = p->softcap;
   kp.lse = p->lse;
   kp.lse_sn = p->lse_stride[0];
@@ -303,11 +361,11 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream) {
   kp.rms_norm = p->diff_rms_norm;
   kp.rms_eps = p->diff_rms_eps;
   kp.status = p->status;
-#ifdef FLB_TRACE
-  kp.trace = g_trace;
-  kp.trace_ctas = g_trace_ctas;
-#endif
-  const int rows_per_cta = p->diff ? kTileM : 2 * kTileM;
+  kp.status_host = p->status_host;
+  kp.wait_limit_us = p->wait_limit_us ? p->wait_limit_us : kDefaultWaitLimitUs;
+  kp.withhold_loads = withhold_loads ? 1 : 0;
+  const int stages = pick_stages(p);
+  const int rows_per_cta = (p->diff || stages == 1) ? kTileM : 2 * kTileM;
   kp.nq_blocks = (p->L + rows_per_cta - 1) / rows_per_cta;
 
   if (p->mask == FLB200_MASK_DOCUMENT) {
@@ -323,8 +381,10 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream) {
   }
 
   // tensor maps: innermost feature axis, then row, head, batch
-  const uint32_t kbox = p->E >= 64 ? 64 : p->E;
-  const uint32_t vbox = p->Ev >= 64 ? 64 : p->Ev;
+  const int width = kernel_width(p->E, p->Ev, p->score_mod, p->mask, p->diff);  // q/k width
+  const int vwidth = p->diff ? 2 * width : width;
+  const uint32_t kbox = width >= 64 ? 64 : width;
+  const uint32_t vbox = vwidth >= 64 ? 64 : vwidth;
   const int Hv = p->diff ? H : p->Hkv;
   CUtensorMap tmQ, tmK, tmV, tmO;
   if (make_tmap_bf16_4d(&tmQ, p->q, p->E, p->L, p->Hq, p->N, p->q_stride[2], p->q_stride[1],
@@ -363,19 +423,22 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream) {
   cudaError_t e = cudaErrorInvalidValue;
   const int sc = p->score_mod, mk = p->mask;
   if (p->diff) {
-    if (p->E == 64) e = dispatch_mods<64, 128, true>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else e = dispatch_mods<32, 64, true>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-  } else if (p->E == 128) {
-    e = dispatch_mods<128, 128, false>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-  } else if (p->E == 64) {
-    e = dispatch_mods<64, 64, false>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    if (width == 64) e = dispatch_mods<64, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    else e = dispatch_mods<32, 64, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+  } else if (stages == 2) {
+    if (width == 128) e = dispatch_mods<128, 128, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    else e = dispatch_mods<32, 32, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
   } else {
-    e = dispatch_mods<32, 32, false>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    if (width == 128) e = dispatch_mods<128, 128, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    else e = dispatch_mods<32, 32, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
   }
   if (e != cudaSuccess) return FLB200_E_LAUNCH;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FLB200_OK;
 }
+}  // namespace
 
 int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream) {
   if (!p || p->struct_size != sizeof(flb200_attn_params)) return FLB200_E_BAD_ARG;
@@ -383,6 +446,12 @@ int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream) {
   if (q.mask == FLB200_MASK_DOCUMENT) {
     if (q.N <= 0 || q.L <= 0 || q.S <= 0) return FLB200_E_BAD_ARG;
     if (map_layout(&q).total > FLB200_NOALLOC_SCRATCH_BYTES) return FLB200_E_WORKSPACE;
+    // argument errors come before anything that needs the device; the workspace fields are
+    // stand-ins until the array's address is known
+    q.workspace = reinterpret_cast<void*>(static_cast<uintptr_t>(256));
+    q.workspace_bytes = FLB200_NOALLOC_SCRATCH_BYTES;
+    const int v = validate(&q);
+    if (v != FLB200_OK) return v;
     const int a = check_arch();
     if (a != FLB200_OK) return a;
     void* scratch = noalloc_scratch_ptr();
@@ -402,13 +471,5 @@ int flb200_decode_status(int32_t status_word, int32_t* barrier, int32_t* block) 
 }
 
 uint64_t flb200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
-
-#ifdef FLB_TRACE
-// tuning builds only: device buffer of ctas * 8 * 128 uint64 that the next launches fill
-void flb200_set_trace(void* device_buffer, int ctas) {
-  g_trace = static_cast<unsigned long long*>(device_buffer);
-  g_trace_ctas = ctas;
-}
-#endif
 
 }  // extern "C"

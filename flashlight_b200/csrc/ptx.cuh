@@ -32,6 +32,11 @@ FLB_DEV bool elect_one() {
   return pred != 0;
 }
 
+// Named barrier `id` (1..15; 0 is __syncthreads) over `count` threads (a multiple of 32).
+FLB_DEV void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 FLB_DEV uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -69,25 +74,34 @@ FLB_DEV bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Upper bound on any single wait inside a kernel.  A legitimate wait covers at
-// most a few tiles of work (microseconds); two seconds means a lost signal.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Upper bound on any single wait inside a kernel unless the launch sets its own.  A legitimate
+// wait covers at most a few tiles of work (microseconds); two seconds means a lost signal.
+constexpr uint32_t kDefaultWaitLimitUs = 2000000u;
 
-// Bounded wait.  `abort_flag` lives in shared memory and is set by whichever
-// thread gives up first, so the other roles stop waiting soon after.
-FLB_DEV bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Per-CTA wait control block in shared memory: the abort flag is raised by whichever thread gives
+// up first, so the other roles stop waiting soon after; `fail_bar` keeps the id of the first
+// barrier that was given up on; `limit_us` is the launch's wait limit.
+struct WaitCtl {
+  volatile int abort;
+  int fail_bar;
+  uint32_t limit_us;
+};
+
+// Bounded wait: false when the limit ran out here or another thread of the CTA already gave up.
+FLB_DEV bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl* ctl) {
 #pragma unroll 1
   for (int i = 0; i < 64; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
+    if (ctl->abort) return false;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      ctl->abort = 1;
       return false;
     }
   }
@@ -156,55 +170,19 @@ FLB_DEV void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: 
 //   [61,64) swizzle: 0 none, 2 = 128 B, 4 = 64 B, 6 = 32 B
 constexpr uint32_t kSwz128 = 2, kSwz64 = 4, kSwz32 = 6, kSwzNone = 0;
 
-FLB_DEV uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                uint32_t swizzle) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(swizzle & 7) << 61;
-  return d;
-}
-
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 //   [4,6) D format (1 = f32)  [7,10) A format (1 = bf16)  [10,13) B format
 //   [15] A major (0 = K)      [16] B major (1 = MN)       [17,23) N >> 3   [24,29) M >> 4
-constexpr uint32_t kFmtF16 = 0, kFmtBF16 = 1;
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N, uint32_t a_fmt, uint32_t b_fmt,
-                                                  int a_mn_major, int b_mn_major) {
-  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
-         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
-         (static_cast<uint32_t>(M >> 4) << 24);
-}
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major,
                                                        int b_mn_major) {
-  return make_idesc(M, N, kFmtBF16, kFmtBF16, a_mn_major, b_mn_major);
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
+         (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(N >> 3) << 17) |
+         (static_cast<uint32_t>(M >> 4) << 24);
 }
 
 // ----------------------------------------------------------------------------
 // tcgen05.mma (single issuing thread), commit
 // ----------------------------------------------------------------------------
-// D[tmem] (+)= A[smem] * B[smem]
-FLB_DEV void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                     uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-FLB_DEV void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                     uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // Forms for the issue loops.  The whole MMA warp runs the loop converged, so that address
 // arithmetic stays on the uniform datapath; only the tensor-core instruction itself is
 // predicated on the elected lane (`leader` != 0 in exactly one lane).  The descriptors differ
@@ -243,13 +221,6 @@ FLB_DEV void umma_commit_c(uint32_t leader, uint32_t bar) {
       ::"r"(bar), "r"(leader)
       : "memory");
 }
-// Arrive on `bar` once every tcgen05 operation issued so far by this thread is done.
-FLB_DEV void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
-
 // ----------------------------------------------------------------------------
 // TMEM <-> registers, shape 32x32b: lane i of the warp owns TMEM lane
 // (warp_id % 4) * 32 + i and receives N consecutive 32-bit columns.
@@ -405,13 +376,6 @@ FLB_DEV float max3(float a, float b, float c) {
 FLB_DEV uint32_t pack_bf16(float lo, float hi) {
   uint32_t y;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
-  return y;
-}
-
-// {lo, hi} -> packed f16x2 with lo in bits [0,16)
-FLB_DEV uint32_t pack_f16(float lo, float hi) {
-  uint32_t y;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
   return y;
 }
 

@@ -20,6 +20,7 @@ import torch
 from . import _lib
 
 _STATUS: dict[int, torch.Tensor] = {}
+_STATUS_HOST: dict[int, torch.Tensor] = {}
 _MAP_CACHE: dict[tuple, tuple] = {}
 _MAP_CACHE_MAX = 8
 
@@ -42,6 +43,17 @@ def _status_word(device: torch.device) -> torch.Tensor:
     return t
 
 
+def _status_mirror(device: torch.device) -> torch.Tensor:
+    """Pinned host copy of the status word: a kernel that gives up also stores the word here, so
+    the next call on the device sees it without synchronising."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _STATUS_HOST.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _STATUS_HOST[idx] = t
+    return t
+
+
 def check_status(device: Optional[torch.device] = None) -> None:
     """Synchronise and raise if a device-side bounded wait expired since the last check."""
     if device is None:
@@ -50,6 +62,7 @@ def check_status(device: Optional[torch.device] = None) -> None:
     word = int(t.item())
     if word != 0:
         t.zero_()
+        _status_mirror(device).zero_()
         bar, blk = C.c_int32(0), C.c_int32(0)
         code = _lib.load().flb200_decode_status(word, C.byref(bar), C.byref(blk))
         raise RuntimeError(
@@ -75,6 +88,11 @@ def _fill_bias(p: _lib.AttnParams, slot: int, b: Optional[torch.Tensor], keep: l
         raise ValueError("flb200: a bias must be 5-D [b, r, h, L, S] (broadcast by expand)")
     if b.dtype != torch.bfloat16:
         raise NotImplementedError("flb200: biases must be bfloat16")
+    if b.size(4) > 1 and b.stride(4) == 0:
+        # broadcast along the keys (evoformer.py:26-27 accepts it): write that axis out, keeping the
+        # zero strides of every other broadcast axis
+        core = b[tuple(slice(0, 1) if b.stride(i) == 0 else slice(None) for i in range(5))]
+        b = core.expand(core.shape[:4] + (b.size(4),)).contiguous().expand(b.shape)
     if b.stride(4) != 1 and b.size(4) != 1:
         raise ValueError("flb200: the key axis of a bias must be contiguous")
     keep.append(b)
@@ -86,7 +104,7 @@ def _fill_bias(p: _lib.AttnParams, slot: int, b: Optional[torch.Tensor], keep: l
 @torch.library.custom_op("flb200::attn_fwd", mutates_args=())
 def attn_fwd(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-    score_mod: int, alibi_heads: int, softcap: float,
+    score_mod: int, alibi_heads: int, alibi_head0: int, softcap: float,
     mask: int, causal: bool, window: int,
     prefix_len: Optional[torch.Tensor], prefix_scalar: int,
     document_id: Optional[torch.Tensor],
@@ -99,12 +117,12 @@ def attn_fwd(
     Returns [N,Ho,L,Ev]; with `rows_major_out` the storage order is [N,L,Ho,Ev] (the
     Evoformer layout) and the returned tensor is the transposed view of it.
     """
-    return _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal, window,
+    return _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap, mask, causal, window,
                           prefix_len, prefix_scalar, document_id, bias0, bias1, bias_inner,
                           diff, diff_lambda, diff_rms_norm, diff_rms_eps, rows_major_out, None)
 
 
-def attn_fwd_lse(q, k, v, scale, *, score_mod=_lib.SCORE_NONE, alibi_heads=0, softcap=0.0,
+def attn_fwd_lse(q, k, v, scale, *, score_mod=_lib.SCORE_NONE, alibi_heads=0, alibi_head0=0, softcap=0.0,
                  mask=_lib.MASK_NONE, causal=False, window=0, prefix_len=None, prefix_scalar=0,
                  document_id=None, bias0=None, bias1=None, bias_inner=1):
     """Forward pass that also returns the log-sum-exp of every query row, fp32 [N, Hq, L] (what a
@@ -112,13 +130,13 @@ def attn_fwd_lse(q, k, v, scale, *, score_mod=_lib.SCORE_NONE, alibi_heads=0, so
     the `flb200::attn_fwd` op without the differential / layout options; not traceable by
     `torch.compile`."""
     lse = torch.empty((q.size(0), q.size(1), q.size(2)), dtype=torch.float32, device=q.device)
-    o = _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal, window,
+    o = _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap, mask, causal, window,
                        prefix_len, prefix_scalar, document_id, bias0, bias1, bias_inner,
                        False, 0.0, False, 0.0, False, lse)
     return o, lse
 
 
-def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal, window,
+def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap, mask, causal, window,
                    prefix_len, prefix_scalar, document_id, bias0, bias1, bias_inner,
                    diff, diff_lambda, diff_rms_norm, diff_rms_eps, rows_major_out, lse):
     lib = _lib.load()
@@ -153,6 +171,7 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal
     p.scale = float(scale)
     p.score_mod = int(score_mod)
     p.alibi_heads = int(alibi_heads)
+    p.alibi_head0 = int(alibi_head0)
     p.softcap = float(softcap)
     _fill_bias(p, 0, bias0, keep)
     _fill_bias(p, 1, bias1, keep)
@@ -171,6 +190,12 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal
     p.diff_rms_norm = int(diff_rms_norm)
     p.diff_rms_eps = float(diff_rms_eps)
     p.status = _status_word(q.device).data_ptr()
+    mirror = _status_mirror(q.device)
+    if int(mirror[0]) != 0:
+        # an earlier launch on this device gave up on a wait; every launch after it ends at once
+        # until the word is cleared, so say so now instead of returning undefined results
+        check_status(q.device)
+    p.status_host = mirror.data_ptr()
     if lse is not None:
         p.lse = lse.data_ptr()
         p.lse_stride[0], p.lse_stride[1] = lse.stride(0), lse.stride(1)
@@ -196,16 +221,25 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal
                    bool(causal), q.device.index)
             hit = _MAP_CACHE.get(key)
             ws = hit[0] if hit is not None else None
+            cur = torch.cuda.current_stream(q.device)
             if ws is None or ws.numel() < nbytes:
                 ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=q.device)
                 p.workspace, p.workspace_bytes, p.block_map_ready = ws.data_ptr(), ws.numel(), 0
                 rc = lib.flb200_build_block_map(C.byref(p), C.c_void_p(stream))
                 if rc != _lib.OK:
                     _raise_for(rc, "build_block_map")
+                built = torch.cuda.Event()
+                built.record(cur)
                 if len(_MAP_CACHE) >= _MAP_CACHE_MAX:
                     _MAP_CACHE.pop(next(iter(_MAP_CACHE)))
                 # the entry keeps `doc` alive, so its address cannot be handed to other ids
-                _MAP_CACHE[key] = (ws, doc)
+                _MAP_CACHE[key] = (ws, doc, built, cur)
+            else:
+                # the map may have been built on another stream: order this launch after the build
+                if hit[3] != cur:
+                    cur.wait_event(hit[2])
+            # an evicted map must not return to the allocator while a kernel of this stream reads it
+            ws.record_stream(cur)
             keep.append(ws)
             p.workspace, p.workspace_bytes, p.block_map_ready = ws.data_ptr(), ws.numel(), 1
         rc = lib.flb200_attn_fwd(C.byref(p), C.c_void_p(stream))
@@ -215,7 +249,7 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal
 
 
 @attn_fwd.register_fake
-def _attn_fwd_fake(q, k, v, scale, score_mod, alibi_heads, softcap, mask, causal, window,
+def _attn_fwd_fake(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap, mask, causal, window,
                    prefix_len, prefix_scalar, document_id, bias0, bias1, bias_inner,
                    diff, diff_lambda, diff_rms_norm, diff_rms_eps, rows_major_out):
     N, Hq, L, _ = q.shape

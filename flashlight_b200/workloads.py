@@ -141,6 +141,61 @@ def io_bytes(w: Workload, t: Dict[str, torch.Tensor]) -> int:
     return sum(v.numel() * v.element_size() for v in t.values())
 
 
+def hbm_bytes(w: Workload, t: Dict[str, torch.Tensor]) -> int:
+    """Compulsory HBM traffic of one forward: every input read once, the result written once."""
+    return io_bytes(w, t) + output_bytes(w)
+
+
+def shard(w: Workload, t: Dict[str, torch.Tensor], rank: int, world: int):
+    """Rank `rank`'s contiguous slice of the workload's independent units, as (workload, tensors).
+
+    Units are the (batch, kv head) pairs in row-major order (MSA rows for Evoformer, (batch, output
+    head) for differential attention): whole sequences when the batch divides over the ranks,
+    otherwise a group of heads of one sequence.  Per-sequence inputs (document ids, prefix
+    lengths, the pair bias) are replicated; ALiBi keeps its slopes through the head offset.  The
+    slices are disjoint, cover every unit, and carry equal work for the benchmark configurations.
+    """
+    if world == 1:
+        return w, t
+    if w.variant == "evoformer":
+        if w.N % world:
+            raise ValueError(f"{w.N} MSA rows do not divide over {world} ranks")
+        r0, r1 = rank * w.N // world, (rank + 1) * w.N // world
+        out = {k: (v[:, r0:r1].contiguous() if v.size(1) == w.N else v) for k, v in t.items()}
+        return w.scaled(N=r1 - r0), out
+    if w.N % world == 0:
+        n0, n1 = rank * w.N // world, (rank + 1) * w.N // world
+        return w.scaled(N=n1 - n0), {k: v[n0:n1].contiguous() for k, v in t.items()}
+    if world % w.N:
+        raise ValueError(f"batch {w.N} and {world} ranks: neither divides the other")
+    c = world // w.N                        # ranks per sequence
+    b, j = rank // c, rank % c
+    H_out = w.Hq // 2 if w.variant == "diff" else w.Hkv
+    if H_out % c:
+        raise ValueError(f"{H_out} heads do not divide over {c} ranks per sequence")
+    hk = H_out // c                         # kv (or output) heads of this rank
+    out: Dict[str, torch.Tensor] = {}
+    if w.variant == "diff":
+        H = w.Hq // 2
+        sel = list(range(j * hk, (j + 1) * hk)) + list(range(H + j * hk, H + (j + 1) * hk))
+        out["q"] = t["q"][b:b + 1, sel].contiguous()
+        out["k"] = t["k"][b:b + 1, sel].contiguous()
+        out["v"] = t["v"][b:b + 1, j * hk:(j + 1) * hk].contiguous()
+        return w.scaled(N=1, Hq=2 * hk, Hkv=2 * hk), out
+    G = w.Hq // w.Hkv
+    out["q"] = t["q"][b:b + 1, j * hk * G:(j + 1) * hk * G].contiguous()
+    out["k"] = t["k"][b:b + 1, j * hk:(j + 1) * hk].contiguous()
+    out["v"] = t["v"][b:b + 1, j * hk:(j + 1) * hk].contiguous()
+    for name in ("document_id", "prefix_len"):
+        if name in t:
+            out[name] = t[name][b:b + 1].contiguous()
+    extra = dict(w.extra)
+    if w.variant == "alibi":
+        extra.update(alibi_heads=w.extra.get("alibi_heads", w.Hq),
+                     alibi_head0=w.extra.get("alibi_head0", 0) + j * hk * G)
+    return w.scaled(N=1, Hq=hk * G, Hkv=hk, extra=extra), out
+
+
 def output_bytes(w: Workload) -> int:
     heads = w.Hq // 2 if w.variant == "diff" else w.Hq
     return w.N * heads * w.S * w.Ev * 2
@@ -155,8 +210,9 @@ def run(w: Workload, t: Dict[str, torch.Tensor]) -> torch.Tensor:
     if w.variant == "causal":
         return av.attention_pytorch_causal(q, k, v, enable_gqa=gqa)
     if w.variant == "alibi":
-        return av.attention_pytorch_alibi(q, k, v, score_mod=av.generate_alibi_bias_pytorch(w.Hq),
-                                          is_causal=w.causal, enable_gqa=gqa)
+        sm = av.AlibiScoreMod(w.extra.get("alibi_heads", w.Hq), head_offset=w.extra.get("alibi_head0", 0),
+                              head_count=w.Hq)
+        return av.attention_pytorch_alibi(q, k, v, score_mod=sm, is_causal=w.causal, enable_gqa=gqa)
     if w.variant == "softcap":
         return av.attention_softcapped(q, k, v, av.generate_tanh_softcap(w.extra["cap"]),
                                        is_causal=w.causal, enable_gqa=gqa)

@@ -21,9 +21,13 @@
  * here is plain C: pointers, sizes, strides.  All tensor pointers are DEVICE
  * pointers to bf16 data; the caller owns every buffer (inputs, output,
  * workspace, status word).  The library allocates no device memory and keeps
- * no pointer after a call returns.  Functions never throw or abort: they
- * return 0 or a negative flb200_status.  Calls are thread-safe and may be
- * issued concurrently on different streams and devices.
+ * no pointer after a call returns; the one exception is flb200_attn_fwd_noalloc,
+ * which works in a static device array of the library and remembers that
+ * array's address per device.  Functions never throw or abort: they return 0 or
+ * a negative flb200_status.  Calls are thread-safe and may be issued
+ * concurrently on different streams and devices; again flb200_attn_fwd_noalloc
+ * is the exception (its calls on one device share the array and must not
+ * overlap on the GPU, see below).
  */
 #ifndef FLB200_ATTN_H_
 #define FLB200_ATTN_H_
@@ -35,7 +39,7 @@
 extern "C" {
 #endif
 
-#define FLB200_ABI_VERSION 2u
+#define FLB200_ABI_VERSION 3u
 
 /* Size of the library-owned scratch behind flb200_attn_fwd_noalloc. */
 #define FLB200_NOALLOC_SCRATCH_BYTES (1u << 20)
@@ -131,7 +135,9 @@ typedef struct flb200_attn_params {
 
   /* Optional device int32, zeroed by the caller.  Non-zero after the stream
    * synchronises means a bounded device-side wait expired (see
-   * flb200_decode_status); outputs are then undefined. */
+   * flb200_decode_status); outputs are then undefined.  The word is sticky: while it is non-zero
+   * every CTA of every later launch that is given the same word ends at once, so that a broken
+   * launch drains quickly; the caller clears it after reading it. */
   int32_t* status;
 
   /* Optional output for a later backward pass (the reference stubs its backward,
@@ -140,6 +146,22 @@ typedef struct flb200_attn_params {
    * -inf for a row without a visible key.  NULL = not wanted.  Not available with `diff`. */
   float* lse;
   int64_t lse_stride[2];
+
+  /* Limit of every device-side wait in microseconds; 0 = the default of two seconds.  A wait
+   * that runs out ends the launch early through the kernels' common exit (tensor memory freed,
+   * status word written); nothing traps or spins without bound. */
+  uint32_t wait_limit_us;
+
+  /* Optional second home of the status word: a device-accessible pointer to pinned (mapped) HOST
+   * memory, zeroed by the caller.  A CTA that gives up stores the status word here as well, so
+   * host code can notice a failed launch by reading host memory, without synchronising.  NULL =
+   * not wanted. */
+  int32_t* status_host;
+
+  /* ALIBI: index of this call's first query head within the alibi_heads heads of the slope
+   * formula (head h of the call uses slope index alibi_head0 + h).  0 unless the heads of one
+   * model are split over several calls. */
+  int32_t alibi_head0;
 } flb200_attn_params;
 
 /* ABI version of the loaded library (FLB200_ABI_VERSION it was built with). */
@@ -187,9 +209,20 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream);
  */
 int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream);
 
+/*
+ * Self-test of the bounded device-side waits.  Launches the forward kernel of `p` with its
+ * loads withheld, so that every role's first wait runs into p->wait_limit_us (0 = 1000 us
+ * here) and the CTAs leave through the common exit: tensor memory is freed, p->status (required)
+ * receives the timeout code, the output is left untouched, the context stays usable.  Returns
+ * FLB200_OK when the launch was enqueued; the caller then synchronises and decodes p->status,
+ * which must read FLB200_E_TIMEOUT.  No counterpart in the reference.
+ */
+int flb200_selftest_wait_timeout(const flb200_attn_params* p, void* cuda_stream);
+
 /* Map the value read back from a status word to a flb200_status
  * (0 -> FLB200_OK, timeout code -> FLB200_E_TIMEOUT).  If `barrier` / `block`
- * are non-NULL they receive which wait expired and in which thread block. */
+ * are non-NULL they receive which wait expired and the low 16 bits of the index of the thread
+ * block that gave up first. */
 int flb200_decode_status(int32_t status_word, int32_t* barrier, int32_t* block);
 
 /* Number of kernels this library has launched since it was loaded (attention

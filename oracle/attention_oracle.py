@@ -109,7 +109,7 @@ def alibi_slopes(nheads: int, device, dtype=torch.float32) -> torch.Tensor:
     return torch.exp2(-((torch.arange(nheads, dtype=torch.int32, device=device) + 1) * 8.0 / nheads)).to(dtype)
 
 
-def alibi(query, key, value, nheads=None, is_causal=False, scale=None, enable_gqa=False, **kw):
+def alibi(query, key, value, nheads=None, is_causal=False, scale=None, enable_gqa=False, head_offset=0, **kw):
     """attention_pytorch_alibi (alibi.py:13-33): score * scale + slope_h * (j - i).
 
     The slope index is the query head (alibi.py:27-28 views the bias as (Hkv, G, L, S)).
@@ -119,7 +119,9 @@ def alibi(query, key, value, nheads=None, is_causal=False, scale=None, enable_gq
     L, S = query.size(-2), key.size(-2)
     H = query.size(1) if nheads is None else nheads
     dtype = kw.get("dtype", torch.float32)
-    slopes = alibi_slopes(H, query.device, dtype)
+    # `head_offset`: the query holds heads [head_offset, head_offset + Hq) of the H heads (a slice
+    # of the reference's [H, L, S] bias, for workloads whose heads are split over several GPUs)
+    slopes = alibi_slopes(H, query.device, dtype)[head_offset:]
     j = torch.arange(S, device=query.device, dtype=torch.int32).view(1, 1, S)
 
     def mod(s, n, h0, h1, l0, l1):

@@ -24,7 +24,12 @@ def good(**over):
         a[0], a[1], a[2] = 4 * 256 * 128, 256 * 128, 128
     p.scale = 0.088
     for k, v in over.items():
-        setattr(p, k, v)
+        if isinstance(v, tuple):
+            arr = getattr(p, k)
+            for i, x in enumerate(v):
+                arr[i] = x
+        else:
+            setattr(p, k, v)
     return p
 
 
@@ -36,8 +41,8 @@ def test_header_symbols_are_exported(lib):
 
 
 def test_abi_version_and_struct_size(lib):
-    assert lib.flb200_abi_version() == 2
-    assert int(re.search(r"#define FLB200_ABI_VERSION (\d+)u", HEADER).group(1)) == 2
+    assert lib.flb200_abi_version() == 3
+    assert int(re.search(r"#define FLB200_ABI_VERSION (\d+)u", HEADER).group(1)) == 3
     p = good()
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
     p.struct_size -= 4
@@ -65,15 +70,32 @@ def test_strerror_distinct(lib):
     (dict(mask=_lib.MASK_SLIDING, window=-1), _lib.E_BAD_ARG),
     (dict(mask=_lib.MASK_SLIDING, window=8, S=128), _lib.E_BAD_ARG),  # L != S
     (dict(mask=_lib.MASK_DOCUMENT), _lib.E_BAD_ARG),                 # no ids
-    (dict(E=96, Ev=96), _lib.E_UNSUPPORTED),
-    (dict(E=128, Ev=64), _lib.E_UNSUPPORTED),
     (dict(E=256, Ev=256), _lib.E_UNSUPPORTED),
+    (dict(E=136, Ev=64), _lib.E_UNSUPPORTED),
+    (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE + 4), _lib.E_MISALIGNED),
+    (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE, N=70000), _lib.E_UNSUPPORTED),
+    (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE, doc_stride_n=8), _lib.E_BAD_ARG),   # rows of L ids overlap
+    (dict(lse=FAKE + 2), _lib.E_MISALIGNED),
+    (dict(lse=FAKE, lse_stride=(16, 8)), _lib.E_BAD_ARG),                                # rows of L floats overlap
     (dict(score_mod=_lib.SCORE_ALIBI, alibi_heads=4, mask=_lib.MASK_SLIDING, window=4), _lib.E_UNSUPPORTED),
     (dict(q=FAKE + 2), _lib.E_MISALIGNED),
     (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE), _lib.E_WORKSPACE),
 ])
 def test_validate_rejects(lib, over, code):
     assert lib.flb200_attn_validate(C.byref(good(**over))) == code
+
+
+@pytest.mark.parametrize("E,Ev", [(96, 96), (128, 64), (64, 128), (48, 16), (8, 8), (120, 128)])
+def test_narrow_and_unequal_head_dims_run_on_the_next_wider_kernel(lib, E, Ev):
+    """Any head dims up to 128 are served: the tensor maps zero-fill the missing feature columns."""
+    p = good(E=E, Ev=Ev)
+    for name, w in (("q_stride", E), ("k_stride", E), ("v_stride", Ev), ("o_stride", Ev)):
+        arr = getattr(p, name)
+        arr[2], arr[1], arr[0] = w, w * 256, w * 256 * p.Hq
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
+    # ALiBi has no 32-wide kernel of its own: it runs on the 64-wide one
+    p.score_mod, p.alibi_heads = _lib.SCORE_ALIBI, p.Hq
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
 
 
 def test_stride_alignment(lib):
@@ -90,7 +112,7 @@ def test_diff_shapes(lib):
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
     p = good(diff=1, E=64, Ev=128, Hq=8, Hkv=4)
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.E_BAD_ARG
-    p = good(diff=1, E=128, Ev=256, Hq=8, Hkv=8)   # the reference's d=128 test shape: V too wide for TMEM
+    p = good(diff=1, E=128, Ev=512, Hq=8, Hkv=8)
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.E_UNSUPPORTED
 
 

@@ -2,7 +2,8 @@
 against the reference's golden outputs and the fp32 oracle.
 
 Tolerances (bf16 output vs fp32 oracle on the same bf16-rounded inputs):
-  N(0,1) inputs:  max-abs <= 2e-2 and mean-abs <= 2e-3
+  N(0,1) inputs:  max-abs <= 2e-2 and mean-abs <= 2e-3 (flat; see tests/_parity.py for the
+                  handling of the rare reference values of magnitude 4 and more)
   U[-9,9) inputs (the reference tests' distribution, tests/test_causal.py:28-30):
                   |a-b| <= 2e-2 + 1e-2 |b|   (tests/test_vanilla.py:36)
 """
@@ -16,34 +17,22 @@ from flashlight_b200 import attention_variants as av
 from flashlight_b200.workloads import WORKLOADS, make_inputs, run as run_product
 from oracle import attention_oracle as ao
 from oracle.run_config import run_oracle
+from _parity import check, report
 
 pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
-MAX_ABS, MEAN_ABS = 2e-2, 2e-3
+
+
+@pytest.fixture(params=[2, 1], ids=["two_stage", "one_stage"])
+def stages(request, monkeypatch):
+    """Run a test with both kernel layouts (two query tiles per CTA, or one and two CTAs per SM)
+    instead of the layout the library would pick for the shape."""
+    monkeypatch.setenv("FLB200_STAGES", str(request.param))
+    return request.param
 
 
 def dev(t):
     return t.cuda() if torch.is_tensor(t) else t
-
-
-def check(out, ref, what=""):
-    """bf16 result against the fp32 oracle: max-abs <= 2e-2, mean-abs <= 2e-3.
-
-    The output itself is bf16 (8 significant bits): writing an exact fp32 value v costs up to half a
-    unit in the last place, which is 2**-8 * |v| at the bottom of a binade (1.6e-2 at |v| = 4, most
-    of the 2e-2 band before any arithmetic error).  The band is therefore taken on top of that
-    unavoidable rounding: |out - ref| <= 2e-2 + 2**-8 * |ref|, which is the plain 2e-2 for the
-    values around 1 that make up nearly all elements and stays inside the reference tests' own
-    atol 2e-2 + rtol 1e-2 (tests/test_vanilla.py:36).
-    """
-    flashlight_b200.check_status()
-    assert out.shape == ref.shape, (what, out.shape, ref.shape)
-    assert out.dtype == torch.bfloat16
-    o, r = out.float().cpu(), ref.float().cpu()
-    d = (o - r).abs()
-    assert torch.isfinite(o).all(), what
-    excess = (d - (MAX_ABS + 2.0 ** -8 * r.abs())).max().item()
-    assert excess <= 0 and d.mean().item() <= MEAN_ABS, (what, d.max().item(), excess, d.mean().item())
 
 
 def load(name):
@@ -51,21 +40,21 @@ def load(name):
 
 
 # ---------------------------------------------------------------- golden vectors
-def test_golden_vanilla():
+def test_golden_vanilla(stages):
     c = load("vanilla_nogqa")
     check(av.attention_pytorch_nogqa(c["q"], c["k"], c["v"]), c["out"])
     c = load("vanilla_gqa")
     check(av.attention_pytorch(c["q"], c["k"], c["v"], enable_gqa=True), c["out"])
 
 
-def test_golden_causal():
+def test_golden_causal(stages):
     c = load("causal")
     check(av.attention_pytorch_causal(c["q"], c["k"], c["v"]), c["out"])
     c = load("causal_gqa")
     check(av.attention_pytorch_causal(c["q"], c["k"], c["v"], enable_gqa=True), c["out"])
 
 
-def test_golden_alibi():
+def test_golden_alibi(stages):
     c = load("alibi")
     check(av.attention_pytorch_alibi(c["q"], c["k"], c["v"], score_mod=av.generate_alibi_bias_pytorch(c["nheads"])),
           c["out"])
@@ -74,23 +63,23 @@ def test_golden_alibi():
                                      enable_gqa=True), c["out"])
 
 
-def test_golden_softcap():
+def test_golden_softcap(stages):
     c = load("softcap")
     check(av.attention_softcapped(c["q"], c["k"], c["v"], av.generate_tanh_softcap(c["cap"])), c["out"])
 
 
-def test_golden_sliding():
+def test_golden_sliding(stages):
     c = load("sliding")
     check(av.attention_pytorch_sliding_window(c["q"], c["k"], c["v"], window_size=c["window"]), c["out"])
 
 
 @pytest.mark.parametrize("name", ["document", "document_unsorted"])
-def test_golden_document(name):
+def test_golden_document(name, stages):
     c = load(name)
     check(av.attention_pytorch_document_mask(c["q"], c["k"], c["v"], c["document_id"]), c["out"])
 
 
-def test_golden_prefix():
+def test_golden_prefix(stages):
     c = load("prefix")
     check(av.attention_pytorch_prefix_lm(c["q"], c["k"], c["v"], prefix_lengths=c["prefix"]), c["out"])
 
@@ -102,7 +91,7 @@ def test_golden_diff(name):
 
 
 @pytest.mark.parametrize("name", ["evoformer", "evoformer_mask"])
-def test_golden_evoformer(name):
+def test_golden_evoformer(name, stages):
     c = load(name)
     check(av.attention_reference(c["q"], c["k"], c["v"], [c["bias1"], c["bias2"]]), c["out"])
 
@@ -118,7 +107,7 @@ def rnd(shape, seed, uniform=False):
 @pytest.mark.parametrize("S", [1, 17, 127, 128, 129, 384, 1000])
 @pytest.mark.parametrize("D", [32, 64, 128])
 @pytest.mark.parametrize("causal", [False, True])
-def test_shapes_vanilla_causal(S, D, causal):
+def test_shapes_vanilla_causal(S, D, causal, stages):
     q, k, v = rnd((2, 3, S, D), 1), rnd((2, 3, S, D), 2), rnd((2, 3, S, D), 3)
     if causal:
         check(av.attention_pytorch_causal(q, k, v), ao.causal(q, k, v), (S, D))
@@ -128,7 +117,7 @@ def test_shapes_vanilla_causal(S, D, causal):
 
 @pytest.mark.parametrize("G", [4, 8])
 @pytest.mark.parametrize("D", [64, 128])
-def test_gqa(G, D):
+def test_gqa(G, D, stages):
     q, k, v = rnd((2, 2 * G, 333, D), 4), rnd((2, 2, 333, D), 5), rnd((2, 2, 333, D), 6)
     out = av.attention_pytorch_causal(q, k, v, enable_gqa=True)
     assert out.shape == (2, 2, G, 333, D)
@@ -148,7 +137,7 @@ def test_cross_attention_lengths():
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("is_causal", [False, True])
-def test_alibi_softcap(D, is_causal):
+def test_alibi_softcap(D, is_causal, stages):
     q, k, v = rnd((2, 8, 700, D), 13), rnd((2, 2, 700, D), 14), rnd((2, 2, 700, D), 15)
     check(av.attention_pytorch_alibi(q, k, v, score_mod=av.generate_alibi_bias_pytorch(8), is_causal=is_causal,
                                      enable_gqa=True),
@@ -160,7 +149,7 @@ def test_alibi_softcap(D, is_causal):
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("shape", ["ramp", "step", "spikes"])
-def test_row_maximum_that_grows_along_the_keys(D, shape):
+def test_row_maximum_that_grows_along_the_keys(D, shape, stages):
     """Later key tiles beat the running maximum by a little (absorbed), by a lot (accumulator
     rescaled) or in single keys: the tile is first tried with the old maximum and must be redone."""
     S = 1280
@@ -182,7 +171,7 @@ def test_row_maximum_that_grows_along_the_keys(D, shape):
 
 
 @pytest.mark.parametrize("S,window", [(1024, 256), (1000, 1), (777, 0), (640, 5000), (1536, 128), (2048, 1024)])
-def test_sliding_window(S, window):
+def test_sliding_window(S, window, stages):
     q, k, v = rnd((1, 2, S, 64), 16), rnd((1, 2, S, 64), 17), rnd((1, 2, S, 64), 18)
     check(av.attention_pytorch_sliding_window(q, k, v, window_size=window),
           ao.sliding_window(q, k, v, window_size=window), (S, window))
@@ -190,7 +179,7 @@ def test_sliding_window(S, window):
 
 @pytest.mark.parametrize("S,D", [(300, 128), (1024, 128), (2500, 128), (1024, 64), (700, 64)])
 @pytest.mark.parametrize("is_causal", [False, True])
-def test_document_mask(S, D, is_causal):
+def test_document_mask(S, D, is_causal, stages):
     q, k, v = rnd((2, 2, S, D), 19), rnd((2, 2, S, D), 20), rnd((2, 2, S, D), 21)
     g = torch.Generator().manual_seed(S)
     lens = []
@@ -207,7 +196,7 @@ def test_document_mask(S, D, is_causal):
 
 
 @pytest.mark.parametrize("S", [256, 1000])
-def test_prefix_lm(S):
+def test_prefix_lm(S, stages):
     q, k, v = rnd((3, 2, S, 64), 22), rnd((3, 2, S, 64), 23), rnd((3, 2, S, 64), 24)
     for p in (0, 1, 256, S):
         check(av.attention_pytorch_prefix_lm(q, k, v, prefix_lengths=p), ao.prefix_lm(q, k, v, prefix_lengths=p), p)
@@ -229,7 +218,7 @@ def test_diff_attention(d, S):
 
 @pytest.mark.parametrize("D", [32, 64, 128])
 @pytest.mark.parametrize("S", [256, 384, 200])
-def test_evoformer(D, S):
+def test_evoformer(D, S, stages):
     B, N, H = 1, 5, 4
     q, k, v = rnd((B, N, S, H, D), 28), rnd((B, N, S, H, D), 29), rnd((B, N, S, H, D), 30)
     pair = rnd((B, 1, H, S, S), 31)
@@ -282,7 +271,7 @@ def test_uniform_inputs_like_reference_tests():
 
 # ---------------------------------------------------------------- properties
 @pytest.mark.parametrize("D", [64, 128])
-def test_a_row_with_one_key_returns_its_value_row_exactly(D):
+def test_a_row_with_one_key_returns_its_value_row_exactly(D, stages):
     """softmax over a single visible key is exactly 1: the row maximum is exact, so P = 1, l = 1 and
     the output row is the bf16 value row, bit for bit (S = 1, and row 0 under a causal mask)."""
     q, k, v = rnd((2, 4, 1, D), 70), rnd((2, 2, 1, D), 71), rnd((2, 2, 1, D), 72)
@@ -309,7 +298,7 @@ def test_deterministic():
         assert torch.equal(av.attention_pytorch_causal(q, k, v), first)
 
 
-def test_strided_inputs_and_layouts():
+def test_strided_inputs_and_layouts(stages):
     """Head-major and row-major storage give the same result (no copies are made)."""
     base = rnd((2, 500, 3, 3 * 64), 53)                   # packed [N, L, H, 3*D]
     q, k, v = (base[..., i * 64:(i + 1) * 64].transpose(1, 2) for i in range(3))
@@ -352,9 +341,10 @@ def test_pinned_host_batches_are_pipelined_and_identical():
 
 
 def test_unsupported_raises_instead_of_falling_back():
-    q = rnd((1, 2, 128, 96), 55)
+    q = rnd((1, 2, 128, 136), 55)                     # head dims above 128 have no kernel
     with pytest.raises(NotImplementedError):
         av.attention_pytorch(q, q, q)
+    q = rnd((1, 2, 128, 64), 55)
     with pytest.raises(NotImplementedError):
         av.attention_pytorch(q.float(), q.float(), q.float())
     before = flashlight_b200.launch_count()
@@ -373,7 +363,9 @@ def test_torch_compile_wraps_the_op():
 @pytest.mark.parametrize("name", [n for n in WORKLOADS if n != "vanilla"])
 def test_full_size_workloads(name):
     """Full benchmark shapes against the fp32 oracle evaluated on the device (the CPU would
-    need minutes); the oracle code is the same, only its tensors live in HBM."""
+    need minutes); the oracle code is the same, only its tensors live in HBM.  The whole batch
+    is computed; the first two sequences (MSA rows) of it are compared, which is the whole
+    batch for the document workload (one sequence)."""
     w = WORKLOADS[name]
     t = {k: v.cuda() for k, v in make_inputs(w, seed=0).items()}
     out = run_product(w, t)
@@ -384,7 +376,11 @@ def test_full_size_workloads(name):
               v[:ws.N] if w.variant != "evoformer" else v) for k, v in t.items()}
     ref = run_oracle(ws, ts)
     got = out[:, :ws.N] if w.variant == "evoformer" else out[:ws.N]
-    check(got, ref, name)
+    s = check(got, ref, name)
+    report(name, s)
+    # the flat figure of the stated tolerance: nothing above 2e-2 except next to a reference value
+    # of 4 or more, whose bf16 rounding alone takes most of that band
+    assert s["n_above_2e-2"] == 0 or s["largest_ref_above_2e-2"] >= 4.0, s
 
 
 def test_vanilla_workload_against_cpu_oracle():

@@ -67,3 +67,62 @@ def test_inputs_are_seeded_and_bf16():
     assert int(a["prefix_len"].max()) <= w.S // 2
     c = make_inputs(w, seed=6)
     assert not torch.equal(a["q"], c["q"])
+
+
+# ---------------------------------------------------------------- slices for several GPUs
+def _small(name):
+    w = WORKLOADS[name]
+    kw = dict(S=96)
+    if w.variant == "evoformer":
+        kw.update(N=8, Hq=2, Hkv=2)
+    elif w.variant == "document":
+        kw.update(N=1, Hq=8, Hkv=8, extra={"doc_min": 10, "doc_max": 40})
+    elif w.variant == "diff":
+        kw.update(N=2, Hq=16, Hkv=16)
+    elif w.variant == "sliding":
+        kw.update(N=2, Hq=8, Hkv=8, extra={"window": 20})
+    else:
+        kw.update(N=2, Hq=16 if w.Hq != w.Hkv else 8, Hkv=4 if w.Hq != w.Hkv else 8)
+    return w.scaled(**kw)
+
+
+@pytest.mark.parametrize("name", [n for n in WORKLOADS if n != "vanilla"])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_slices_are_disjoint_cover_everything_and_reproduce_the_whole(name, world):
+    """Every rank's slice through the oracle, put back together, is the oracle on the whole
+    workload: the slices cover every (batch, head) unit once, per-sequence inputs and the ALiBi
+    slopes travel with them, and the work adds up."""
+    from flashlight_b200.workloads import shard
+    from oracle.run_config import run_oracle
+    w = _small(name)
+    t = make_inputs(w, seed=5)
+    whole = run_oracle(w, t)
+    parts, flops = [], 0.0
+    for rank in range(world):
+        ws, ts = shard(w, t, rank, world)
+        flops += effective_flops(ws, ts)
+        parts.append(run_oracle(ws, ts))
+    assert flops == pytest.approx(effective_flops(w, t), rel=1e-12)
+    if w.variant == "evoformer":
+        got = torch.cat(parts, dim=1)
+    elif w.N % world == 0:
+        got = torch.cat(parts, dim=0)
+    else:
+        c = world // w.N                              # ranks per sequence: head groups of one sequence
+        got = torch.cat([torch.cat(parts[b * c:(b + 1) * c], dim=1) for b in range(w.N)], dim=0)
+    assert got.shape == whole.shape
+    assert torch.equal(got, whole)
+
+
+def test_full_size_slices_carry_equal_work():
+    from flashlight_b200.workloads import shard
+    for name in ("causal_gqa", "alibi_causal", "sliding_window", "diff_attn"):
+        w = WORKLOADS[name]
+        shapes = {k: torch.empty(0) for k in ()}
+        # only shapes matter for these variants' pair counts: use meta tensors
+        t = {"q": torch.empty(w.N, w.Hq, w.S, w.E, device="meta"),
+             "k": torch.empty(w.N, w.Hkv, w.S, w.E, device="meta"),
+             "v": torch.empty(w.N, w.Hq // 2 if w.variant == "diff" else w.Hkv, w.S, w.Ev, device="meta")}
+        for world in (2, 4, 8):
+            per = {effective_flops(*shard(w, t, r, world)) for r in range(world)}
+            assert len(per) == 1 and per.pop() * world == pytest.approx(effective_flops(w, t), rel=1e-12)
