@@ -279,6 +279,10 @@ def time_back_to_back(w, copies, steps, warmup, run_product, lib_count):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n0 = lib_count()
+    # A launch through Python costs tens of microseconds of host time.  The GPU first idles on a
+    # spin kernel while the host queues all K launches, so that the events bracket K kernels
+    # running back to back and not the host's launch rate (it matters for kernels below 0.1 ms).
+    torch.cuda._sleep(int(2.0e6 * (0.5 + 0.1 * steps)))
     start.record()
     for i in range(steps):
         out = run_product(w, copies[i % len(copies)])

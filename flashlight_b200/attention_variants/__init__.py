@@ -2,7 +2,7 @@
 sm_100a kernels."""
 from .vanilla import attention_pytorch, attention_pytorch_nogqa
 from .causal import attention_pytorch_causal
-from .alibi import alibi_bias, attention_pytorch_alibi, generate_alibi_bias_pytorch
+from .alibi import AlibiScoreMod, alibi_bias, attention_pytorch_alibi, generate_alibi_bias_pytorch
 from .softcap import attention_softcapped, generate_tanh_softcap
 from .sliding_window import attention_pytorch_sliding_window, get_sliding_mask
 from .document_mask import attention_pytorch_document_mask, create_document_id
@@ -12,7 +12,7 @@ from .evoformer import attention_reference
 
 __all__ = [
     "attention_pytorch", "attention_pytorch_nogqa", "attention_pytorch_causal",
-    "alibi_bias", "attention_pytorch_alibi", "generate_alibi_bias_pytorch",
+    "AlibiScoreMod", "alibi_bias", "attention_pytorch_alibi", "generate_alibi_bias_pytorch",
     "attention_softcapped", "generate_tanh_softcap",
     "attention_pytorch_sliding_window", "get_sliding_mask",
     "attention_pytorch_document_mask", "create_document_id",

@@ -43,7 +43,7 @@ def reference_runner(w):
     """The reference's OWN eager function for workload `w`, or None.
 
     `oracle/build_ref.py` compiles the reference's `attention_variants/*.py` (where its checkout is
-    mounted) into sourceless modules under `oracle/_ref/`; they are imported from there.  Only
+    mounted) into an archive of sourceless modules under `oracle/_ref/`; they are imported from it.  Only
     workloads the reference's functions compute as they stand qualify (fp32 on the host, as the
     reference's tests run them): the benchmark configurations that add a causal mask to ALiBi,
     softcap or the document mask, tensor prefix lengths, or RMS-normalised differential attention
@@ -52,8 +52,8 @@ def reference_runner(w):
     import importlib
     import sys
     from pathlib import Path
-    root = Path(__file__).resolve().parent / "_ref"
-    if not (root / "attention_variants" / "__init__.pyc").exists():
+    root = Path(__file__).resolve().parent / "_ref" / "attention_variants.bin"
+    if not root.exists():
         return None
     if w.variant not in ("vanilla", "causal", "sliding", "evoformer"):
         return None

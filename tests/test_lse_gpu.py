@@ -34,7 +34,7 @@ def test_vanilla_and_causal(S, D):
     o, lse = ops.attn_fwd_lse(q, k, v, scale, mask=_lib.MASK_CAUSAL)
     check(o, lse, *ao.causal(q, k, v, return_lse=True))
     # the output is the one the plain op returns
-    plain = torch.ops.flb200.attn_fwd(q, k, v, scale, 0, 0, 0.0, _lib.MASK_CAUSAL, False, 0, None, 0, None,
+    plain = torch.ops.flb200.attn_fwd(q, k, v, scale, 0, 0, 0, 0.0, _lib.MASK_CAUSAL, False, 0, None, 0, None,
                                       None, None, 1, False, 0.0, False, 0.0, False)
     assert torch.equal(plain, o)
 

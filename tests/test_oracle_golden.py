@@ -120,3 +120,19 @@ def test_log_sum_exp_output_is_the_logsumexp_of_the_scaled_masked_scores():
     out, lse = ao.vanilla(c["q"], c["k"], c["v"], return_lse=True)
     close(out, c["out"])
     close(lse, torch.logsumexp(q @ k.transpose(-1, -2) / q.size(-1) ** 0.5, dim=-1))
+
+
+@pytest.mark.parametrize("name", ["vanilla", "causal_gqa", "sliding_window", "evoformer"])
+def test_oracle_equals_the_compiled_reference_modules(name):
+    """Where `oracle/_ref/` holds the reference's own byte-compiled modules (built by
+    `oracle/build_ref.py`), the restatement and the reference give the same fp32 result on a
+    shortened benchmark workload, bit for bit."""
+    from flashlight_b200.workloads import WORKLOADS, make_inputs
+    from oracle.run_config import reference_runner, run_oracle
+    w = WORKLOADS[name]
+    w = w.scaled(N=min(w.N, 3), S=200)
+    fn = reference_runner(w)
+    if fn is None:
+        pytest.skip("oracle/_ref has not been built here")
+    t = make_inputs(w, seed=9)
+    assert torch.equal(fn(w, t), run_oracle(w, t))
