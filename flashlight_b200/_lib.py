@@ -25,6 +25,7 @@ E_LAUNCH = -6
 E_TIMEOUT = -7
 
 SCORE_NONE, SCORE_ALIBI, SCORE_SOFTCAP, SCORE_BIAS = 0, 1, 2, 3
+PW_IDENTITY, PW_RELU, PW_TANH, PW_SIGMOID = 0, 1, 2, 3
 MASK_NONE, MASK_CAUSAL, MASK_SLIDING, MASK_PREFIX, MASK_DOCUMENT = 0, 1, 2, 3, 4
 
 ABI_VERSION = 3
@@ -68,6 +69,9 @@ class AttnParams(C.Structure):
         ("wait_limit_us", C.c_uint32),
         ("status_host", C.c_void_p),
         ("alibi_head0", C.c_int32),
+        ("product_chain", C.c_int32),
+        ("pointwise", C.c_int32),
+        ("k_keys_contiguous", C.c_int32),
     ]
 
 

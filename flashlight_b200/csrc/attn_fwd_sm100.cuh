@@ -65,6 +65,9 @@ struct AttnCfg {
 #define FLB_SOFTCAP_EARLY_PV 1
 #endif
   static constexpr bool EARLY_PV = FLB_SOFTCAP_EARLY_PV && SCORE_ == SCORE_SOFTCAP;
+  // back-to-back product O = f(Q K^T * scale) V: no softmax; KT: K arrives as [E][S], keys contiguous
+  static constexpr bool B2B = SCORE_ == SCORE_B2B || SCORE_ == SCORE_B2BT;
+  static constexpr bool KT = SCORE_ == SCORE_B2BT;
   static constexpr int KBOX = E >= 64 ? 64 : E;     // elements per swizzled row of a Q/K box
   static constexpr int VBOX = EV >= 64 ? 64 : EV;   // elements per swizzled row of a V box
   static constexpr int NKB = E / KBOX, NVB = EV / VBOX;
@@ -105,7 +108,7 @@ struct AttnCfg {
 #define FLB_SPECULATE_SEP 1
 #endif
   static constexpr bool SPECULATE = FLB_SPECULATE && !DIFF_ && !EARLY_PV && MASK_ != MASK_DOCUMENT &&
-                                    (FLB_SPECULATE_SEP || !SEP_P);
+                                    !B2B && (FLB_SPECULATE_SEP || !SEP_P);
   static constexpr int COL_P0 = STAGES == 2 ? 384 : 128 + EV, COL_P1 = 448;
   static_assert(!SEP_P || COL_P0 + 64 <= TMEM_COLS, "P columns do not fit");
   static_assert(E % 16 == 0 && EV % 16 == 0, "head dims must be multiples of 16");
@@ -192,6 +195,10 @@ struct Smem {
   FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }
   FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
   FLB_DEV float* scale(int s) const { return reinterpret_cast<float*>(aux() + 512) + s * 128; }
+  // pair exchange (differential attention with value heads of two kernel widths): a barrier the
+  // partner CTA arrives at and the 128 row sums it stores here
+  FLB_DEV uint32_t xbar() const { return smem_u32(aux()) + 280; }
+  FLB_DEV float* xchg() const { return reinterpret_cast<float*>(aux() + 1536); }
 };
 
 #define FLB_WAIT_RET(sm, id, parity, ret)                         \
@@ -215,7 +222,7 @@ struct Smem {
 // ------------------------------------------------------------------------------------------
 template <class C>
 FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensorMap* tmK,
-                       const CUtensorMap* tmV, const KernelParams& p, int n, int h,
+                       const CUtensorMap* tmV, const KernelParams& p, int n, int h, int vcol0,
                        const int (&r0)[2], const TileRange (&rg)[2], int lo, int hi) {
   // wait self-test: nothing is loaded, so the first wait of every other role runs into its limit
   if (p.withhold_loads) return;
@@ -242,12 +249,21 @@ FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensor
       mbar_arrive_expect_tx(sm.bar(BAR_KV_FULL + slot), C::K_BYTES);
       const uint32_t dst = smem_u32(sm.slot(slot));
 #pragma unroll
-      for (int d = 0; d < (C::DIFF ? 2 : 1); ++d) {
-        const int kh = C::DIFF ? kvh + d * p.diff_heads : kvh;
+      if constexpr (C::KT) {
+        // K^T tile: E feature rows of 128 keys, as two boxes of 64 keys (128-byte swizzled rows)
 #pragma unroll
-        for (int kb = 0; kb < C::NKB; ++kb)
-          tma_load_4d(dst + d * C::K_HEAD_BYTES + kb * C::QK_BOX_BYTES, tmK,
-                      sm.bar(BAR_KV_FULL + slot), kb * C::KBOX, t * kTileN, kh, n);
+        for (int kb = 0; kb < 2; ++kb)
+          tma_load_4d(dst + kb * (C::E * 128), tmK, sm.bar(BAR_KV_FULL + slot), t * kTileN + kb * 64, 0,
+                      kvh, n);
+      } else {
+#pragma unroll
+        for (int d = 0; d < (C::DIFF ? 2 : 1); ++d) {
+          const int kh = C::DIFF ? kvh + d * p.diff_heads : kvh;
+#pragma unroll
+          for (int kb = 0; kb < C::NKB; ++kb)
+            tma_load_4d(dst + d * C::K_HEAD_BYTES + kb * C::QK_BOX_BYTES, tmK,
+                        sm.bar(BAR_KV_FULL + slot), kb * C::KBOX, t * kTileN, kh, n);
+        }
       }
       ++seq;
     }
@@ -259,7 +275,7 @@ FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensor
       const uint32_t dst = smem_u32(sm.slot(slot));
 #pragma unroll
       for (int vb = 0; vb < C::NVB; ++vb)
-        tma_load_4d(dst + vb * C::V_BOX_BYTES, tmV, sm.bar(BAR_KV_FULL + slot), vb * C::VBOX,
+        tma_load_4d(dst + vb * C::V_BOX_BYTES, tmV, sm.bar(BAR_KV_FULL + slot), vcol0 + vb * C::VBOX,
                     t * kTileN, kvh, n);
       ++seq;
     }
@@ -277,7 +293,7 @@ template <class C>
 FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                       const TileRange (&rg)[2], int lo, int hi) {
   const uint32_t leader = elect_one() ? 1u : 0u;  // the lane that issues; all lanes run the loop
-  constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, 0);
+  constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, C::KT ? 1 : 0);
   constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
   const uint32_t tS[2] = {tmem + C::COL_S0, tmem + C::COL_S1};
   const uint32_t tO[2] = {tmem + C::COL_O0, tmem + C::COL_O1};
@@ -288,10 +304,20 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
   constexpr uint64_t vdesc0 = (static_cast<uint64_t>((8 * C::VBOX * 2) >> 4) << 32) |
                               (static_cast<uint64_t>(C::V_BOX_BYTES >> 4) << 16) | (1ull << 46) |
                               (static_cast<uint64_t>(C::SWZ_V) << 61);
+  // K^T tile (keys contiguous): an MN-major operand like V; 8-row groups 1024 bytes apart, the two
+  // 64-key boxes E * 128 bytes apart, 128-byte swizzle
+  constexpr uint64_t ktdesc0 = (static_cast<uint64_t>(1024 >> 4) << 32) |
+                               (static_cast<uint64_t>((C::E * 128) >> 4) << 16) | (1ull << 46) |
+                               (static_cast<uint64_t>(kSwz128) << 61);
+  [[maybe_unused]] constexpr uint32_t kt_hi = static_cast<uint32_t>(ktdesc0 >> 32),
+                                      kt_lo0 = static_cast<uint32_t>(ktdesc0);
   constexpr uint32_t k_hi = static_cast<uint32_t>(kdesc0 >> 32), k_lo0 = static_cast<uint32_t>(kdesc0);
   constexpr uint32_t v_hi = static_cast<uint32_t>(vdesc0 >> 32), v_lo0 = static_cast<uint32_t>(vdesc0);
-  const uint32_t q_lo[2] = {k_lo0 + (smem_u32(sm.q(0)) >> 4), k_lo0 + (smem_u32(sm.q(1)) >> 4)};
-  const uint32_t slot0 = smem_u32(sm.slot(0)) >> 4;
+  // (matrix descriptors take the offset inside this CTA's shared memory: in a cluster launch the
+  // shared-window address of every CTA but the first carries its rank in the high bits)
+  const uint32_t q_lo[2] = {k_lo0 + ((smem_u32(sm.q(0)) & 0x3FFFFu) >> 4),
+                            k_lo0 + ((smem_u32(sm.q(1)) & 0x3FFFFu) >> 4)};
+  const uint32_t slot0 = (smem_u32(sm.slot(0)) & 0x3FFFFu) >> 4;
   bool q_ready[2] = {false, false};
 
   // position u of the walk holds tile lo + u (or hi - 1 - u when the walk is reversed); stage s
@@ -369,13 +395,24 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                 tc_fence_after();
               }
             }
-            const uint32_t ks_lo = k_lo + (C::DIFF ? s * (C::K_HEAD_BYTES >> 4) : 0);
-            umma_ss_c<0>(leader, tS[s], q_lo[s], ks_lo, k_hi, idesc_qk);
+            if constexpr (C::KT) {
+              const uint32_t kt_lo = k_lo - k_lo0 + kt_lo0;
+              umma_ss2_c<0>(leader, tS[s], q_lo[s], k_hi, kt_lo, kt_hi, idesc_qk);
 #pragma unroll
-            for (int k = 1; k < C::E / 16; ++k) {
-              const int kk = k * 16;
-              const uint32_t off = ((kk / C::KBOX) * C::QK_BOX_BYTES + (kk % C::KBOX) * 2) >> 4;
-              umma_ss_c<1>(leader, tS[s], q_lo[s] + off, ks_lo + off, k_hi, idesc_qk);
+              for (int k = 1; k < C::E / 16; ++k) {
+                const int kk = k * 16;
+                const uint32_t off = ((kk / C::KBOX) * C::QK_BOX_BYTES + (kk % C::KBOX) * 2) >> 4;
+                umma_ss2_c<1>(leader, tS[s], q_lo[s] + off, k_hi, kt_lo + ((kk * 128) >> 4), kt_hi, idesc_qk);
+              }
+            } else {
+              const uint32_t ks_lo = k_lo + (C::DIFF ? s * (C::K_HEAD_BYTES >> 4) : 0);
+              umma_ss_c<0>(leader, tS[s], q_lo[s], ks_lo, k_hi, idesc_qk);
+#pragma unroll
+              for (int k = 1; k < C::E / 16; ++k) {
+                const int kk = k * 16;
+                const uint32_t off = ((kk / C::KBOX) * C::QK_BOX_BYTES + (kk % C::KBOX) * 2) >> 4;
+                umma_ss_c<1>(leader, tS[s], q_lo[s] + off, ks_lo + off, k_hi, idesc_qk);
+              }
             }
             umma_commit_c(leader, sm.bar(BAR_S_FULL + s));
           }
@@ -840,11 +877,62 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
 }
 
 // ------------------------------------------------------------------------------------------
+// pointwise pass of the back-to-back product (takes the place of the softmax warps): bf16(f(S * scale))
+// goes back to tensor memory as the A operand of the second product; no maximum, no sum, no rescale
+// ------------------------------------------------------------------------------------------
+template <class C>
+FLB_DEV void pointwise_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p, int s, TileRange rg) {
+  const int row = threadIdx.x & 127;
+  const uint32_t lane_base = static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32u;
+  const uint32_t tS = tmem + (s ? C::COL_S1 : C::COL_S0) + (lane_base << 16);
+  const uint32_t tPs = C::SEP_P ? tmem + (s ? C::COL_P1 : C::COL_P0) + (lane_base << 16) : tS;
+  const float2 sc2 = make_float2(p.scale, p.scale);
+#pragma unroll 1
+  for (int it = 0; it < rg.hi - rg.lo; ++it) {
+    FLB_WAIT(sm, BAR_S_FULL + s, it & 1);
+    tc_fence_after();
+    uint32_t v[128];
+    tmem_ld128_sync(tS, v);
+    if constexpr (C::SEP_P) {
+      tc_fence_before();
+      mbar_arrive(sm.bar(BAR_S_FREE + s));
+      if (it > 0) FLB_WAIT(sm, BAR_PV_DONE + s, (it - 1) & 1);
+    }
+    uint32_t pk[64];
+    if (p.pointwise == PW_IDENTITY || p.pointwise == PW_RELU) {
+      const float floor_ = p.pointwise == PW_RELU ? 0.f : -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        const float2 x = __fmul2_rn(make_float2(u2f(v[c]), u2f(v[c + 1])), sc2);
+        pk[c >> 1] = pack_bf16(fmaxf(x.x, floor_), fmaxf(x.y, floor_));
+      }
+    } else {
+      // tanh(x), or sigmoid(x) = 0.5 tanh(x / 2) + 0.5
+      const bool sig = p.pointwise == PW_SIGMOID;
+      const float pre = sig ? 0.5f * p.scale : p.scale, mul = sig ? 0.5f : 1.0f, add = sig ? 0.5f : 0.0f;
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        const float a = fmaf(tanh_approx(u2f(v[c]) * pre), mul, add);
+        const float b = fmaf(tanh_approx(u2f(v[c + 1]) * pre), mul, add);
+        pk[c >> 1] = pack_bf16(a, b);
+      }
+    }
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) tmem_st16(tPs + chunk * 16, pk + chunk * 16);
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(sm.bar(BAR_P_FULL + s));
+  }
+  sm.scale(s)[row] = 1.0f;  // the epilogue's normalisation becomes a copy
+  mbar_arrive(sm.bar(BAR_SCALE_FULL + s));
+}
+
+// ------------------------------------------------------------------------------------------
 // epilogue (one warpgroup serves both stages)
 // ------------------------------------------------------------------------------------------
 template <class C>
 FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* tmO,
-                           const KernelParams& p, int n, int h, const int (&r0)[2],
+                           const KernelParams& p, int n, int h, int vcol0, const int (&r0)[2],
                            const TileRange (&rg)[2], int lo, int hi) {
   const int row = threadIdx.x & 127;
   const uint32_t lane_base = static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32u;
@@ -867,7 +955,7 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
       FLB_WAIT_RET(sm, BAR_O_STAGED + s, 0, false);
 #pragma unroll
       for (int vb = 0; vb < C::NVB; ++vb)
-        tma_store_4d(tmO, smem_u32(tile) + vb * (128 * ROWB), vb * C::VBOX, r_first, h, n);
+        tma_store_4d(tmO, smem_u32(tile) + vb * (128 * ROWB), vcol0 + vb * C::VBOX, r_first, h, n);
       tma_store_commit();
     }
     return true;
@@ -927,7 +1015,19 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
         }
       }
     }
-    const float rs = p.rms_norm ? rsqrtf(ss * (1.0f / C::EV) + p.rms_eps) : 1.0f;
+    if (p.rms_norm && p.v_exchange) {
+      // this CTA holds half of the row's columns: hand the partner this half's sum of squares (a
+      // plain store into its shared memory, then an arrival on its barrier) and take its half
+      const uint32_t partner = cluster_ctarank() ^ 1u;
+      cluster_store_f32(cluster_map(smem_u32(sm.xchg() + row), partner), ss);
+      cluster_mbar_arrive(cluster_map(sm.xbar(), partner));
+      if (!mbar_wait_cluster(sm.xbar(), 0, sm.ctl())) {
+        atomicCAS(&sm.ctl()->fail_bar, -1, static_cast<int>(BAR_COUNT));
+        return;
+      }
+      ss += sm.xchg()[row];
+    }
+    const float rs = p.rms_norm ? rsqrtf(ss * p.inv_ev + p.rms_eps) : 1.0f;
     uint8_t* tile = sm.q(0);  // both Q tiles (2 * 128 * E * 2 bytes = one 128 x EV output tile)
     static_assert(2 * C::Q_BYTES >= 128 * C::EV * 2, "output tile does not fit the Q tiles");
 #pragma unroll
@@ -974,10 +1074,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // same K/V.
   const int bh_count = p.N * p.H;
   const int per_sec = p.sec_bh * p.nq_blocks;
-  const int sec = static_cast<int>(blockIdx.x) / per_sec;
+  // (differential attention with wide value heads: neighbouring CTAs share a work item and take one
+  // half of the value columns each)
+  const int vhalves = C::DIFF ? p.v_halves : 1;
+  const int item = static_cast<int>(blockIdx.x) / vhalves;
+  const int vcol0 = C::DIFF ? (static_cast<int>(blockIdx.x) % vhalves) * C::EV : 0;
+  const int sec = item / per_sec;
   const int bh0 = sec * p.sec_bh;
   const int width = min(p.sec_bh, bh_count - bh0);  // the last section may be narrower
-  const int wi = static_cast<int>(blockIdx.x) - sec * per_sec;
+  const int wi = item - sec * per_sec;
   const int qb = p.nq_blocks - 1 - wi / width;
   const int bh = bh0 + wi % width;
   const int n = bh / p.H, h = bh % p.H;
@@ -1015,6 +1120,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                (lane >= BAR_P_HALF && lane < BAR_KV_FULL) || lane >= BAR_S_FREE;
       mbar_init(sm.bar(lane), all_threads ? 128 : 1);  // 128 arriving threads, or one commit / TMA
     }
+    if (C::DIFF && lane == 0) mbar_init(sm.xbar(), 128);
     fence_mbar_init();
     named_bar_sync(1, 64);
   }
@@ -1037,6 +1143,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tc_fence_after();
     tmem = *sm.tmem_base();
   }
+  // a CTA pair that will exchange row sums: neither may write into the other before its barrier
+  // exists (the producer warp passed the barrier initialisation above, too)
+  if (C::DIFF && p.v_exchange) cluster_sync_all();
   // A launch in which some CTA already gave up is not worth finishing: one thread of the MMA warp's
   // group that has nothing else to do looks at the status word and raises the abort flag, which
   // ends every role at its next long wait.  The look-up stays off the path to the first MMA.
@@ -1047,17 +1156,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp < C::W_SOFTMAX_END) {
     reg_inc<C::STAGES == 2 ? FLB_REGS_SOFTMAX : FLB_REGS_SOFTMAX1>();
     const int s = warp >> 2;
-    if (rg[s].hi > rg[s].lo) softmax_role<C>(sm, tmem, p, s, n, h, r0[s], rg[s]);
+    if (rg[s].hi > rg[s].lo) {
+      if constexpr (C::B2B) pointwise_role<C>(sm, tmem, p, s, rg[s]);
+      else softmax_role<C>(sm, tmem, p, s, n, h, r0[s], rg[s]);
+    }
     // one query tile per CTA: its softmax warps also write the result
-    if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, r0, rg, lo, hi);
+    if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else if (C::STAGES == 2 && warp < 12) {
     reg_dec<FLB_REGS_EPILOGUE>();
-    epilogue_role<C>(sm, tmem, &tmO, p, n, h, r0, rg, lo, hi);
+    epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else {
     reg_dec<C::STAGES == 2 ? FLB_REGS_ISSUE : FLB_REGS_ISSUE1>();
     if (hi > lo) {
       if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi);
-      if (warp == C::W_TMA && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, r0, rg, lo, hi);
+      if (warp == C::W_TMA && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, vcol0, r0, rg, lo, hi);
     }
     __syncwarp();
   }
@@ -1065,6 +1177,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // common exit: every role arrives here, also after a timed-out wait
   tc_fence_before();
   __syncthreads();
+  // a CTA pair leaves together: the partner may still be storing into this CTA's shared memory
+  if (C::DIFF && p.v_exchange) cluster_sync_all();
   if (sm.ctl()->abort) {
     // give loads that are still in flight time to land before shared memory and TMEM go away
     for (int k = 0; k < 64; ++k) __nanosleep(20000);

@@ -11,6 +11,7 @@ namespace flb {
 
 template <int E, int EV, int SCORE, int MASK, bool DIFF, int STAGES>
 cudaError_t launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                        const CUtensorMap& tmO, const KernelParams& p, int grid, cudaStream_t stream);
+                        const CUtensorMap& tmO, const KernelParams& p, int grid, int cluster,
+                        cudaStream_t stream);
 
 }  // namespace flb

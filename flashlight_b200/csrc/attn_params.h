@@ -6,7 +6,18 @@
 
 namespace flb {
 
-enum ScoreMod : int { SCORE_NONE = 0, SCORE_ALIBI = 1, SCORE_SOFTCAP = 2, SCORE_BIAS = 3 };
+enum ScoreMod : int {
+  SCORE_NONE = 0,
+  SCORE_ALIBI = 1,
+  SCORE_SOFTCAP = 2,
+  SCORE_BIAS = 3,
+  // kernel-internal modes (never in the public struct): the back-to-back product
+  // O = f(Q K^T * scale) V without softmax, K given as [S][E] rows or as [E][S] (keys contiguous)
+  SCORE_B2B = 4,
+  SCORE_B2BT = 5
+};
+// pointwise function between the two products of the back-to-back mode
+enum Pointwise : int { PW_IDENTITY = 0, PW_RELU = 1, PW_TANH = 2, PW_SIGMOID = 3 };
 enum MaskKind : int {
   MASK_NONE = 0,
   MASK_CAUSAL = 1,    // keep j <= i
@@ -38,6 +49,7 @@ struct KernelParams {
   float alibi_log2_slope_step;  // -8 / n_heads: slope_h = 2^((alibi_head0 + h + 1) * step)
   int alibi_head0;
   float softcap;      // cap
+  int pointwise;      // Pointwise, back-to-back mode only
   // additive biases (bf16), row pointer = base + b*sb + r*sr + h*sh + i*sl, keys contiguous
   const void* bias[2];
   int64_t bias_sb[2], bias_sr[2], bias_sh[2], bias_sl[2];
@@ -57,6 +69,9 @@ struct KernelParams {
   float lambda;
   int rms_norm;
   float rms_eps;
+  float inv_ev;     // 1 / (true value width): the mean of the RMS normalisation
+  int v_halves;     // 2: value heads wider than the kernel; CTA pairs take one half of the columns each
+  int v_exchange;   // the two CTAs of a pair run as a cluster and swap their rows' sums of squares
   // bookkeeping
   int nq_blocks;   // CTAs along the query axis
   int sec_bh;      // (batch, head) pairs per L2 section: their K/V together fit in L2

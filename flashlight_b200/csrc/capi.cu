@@ -68,6 +68,7 @@ MapLayout map_layout(const flb200_attn_params* p) {
 // carry the true widths, so the loads fill the missing feature columns with zeros (they add nothing
 // to q.k, and the value columns beyond Ev are clipped by the output store).
 bool kernel_built(int D, int score, int mask) {
+  if (score == SCORE_B2B || score == SCORE_B2BT) return mask == MASK_NONE && (D == 32 || D == 64 || D == 128);
   if (D == 32)
     return (score == SCORE_NONE && (mask == MASK_NONE || mask == MASK_CAUSAL)) ||
            (score == SCORE_BIAS && mask == MASK_NONE);
@@ -85,19 +86,28 @@ bool kernel_built(int D, int score, int mask) {
 }
 
 // Width of the kernel that serves (E, Ev): plain variants use one width for q/k and v; the
-// differential kernels come as (q/k width, v width) = (32, 64) and (64, 128), returned as the
-// q/k width.  0 = no kernel.
+// differential kernels come as (q/k width, v width) = (32, 64), (64, 128) and (128, 128 per CTA of
+// a pair), returned as the q/k width.  0 = no kernel.
 int kernel_width(int E, int EV, int score, int mask, int diff) {
   if (diff) {
     if (score != SCORE_NONE || (mask != MASK_NONE && mask != MASK_CAUSAL)) return 0;
     if (E <= 32 && EV <= 64) return 32;
     if (E <= 64 && EV <= 128) return 64;
+    // q/k heads up to 128 with value heads up to 256: two CTAs per work item, one half of the value
+    // columns each (two accumulators of 256 columns and two score tiles exceed tensor memory)
+    if (E <= 128 && EV <= 256) return 128;
     return 0;
   }
   const int need = E > EV ? E : EV;
   for (int D : {32, 64, 128})
     if (D >= need && kernel_built(D, score, mask)) return D;
   return 0;
+}
+
+// kernel-internal score mode of a problem (the product chain has modes of its own)
+int kernel_score(const flb200_attn_params* p) {
+  if (p->product_chain) return p->k_keys_contiguous ? SCORE_B2BT : SCORE_B2B;
+  return p->score_mod;
 }
 
 int validate(const flb200_attn_params* p) {
@@ -148,12 +158,19 @@ int validate(const flb200_attn_params* p) {
       p->L != p->S)
     return FLB200_E_BAD_ARG;
 
-  if (!kernel_width(p->E, p->Ev, p->score_mod, p->mask, p->diff)) return FLB200_E_UNSUPPORTED;
+  if (p->product_chain) {
+    if (p->score_mod != FLB200_SCORE_NONE || p->mask != FLB200_MASK_NONE || p->diff || p->lse)
+      return FLB200_E_BAD_ARG;
+    if (p->pointwise < FLB200_PW_IDENTITY || p->pointwise > FLB200_PW_SIGMOID) return FLB200_E_BAD_ARG;
+  } else if (p->k_keys_contiguous) {
+    return FLB200_E_UNSUPPORTED;  // only the product chain reads K with the keys contiguous
+  }
+  if (!kernel_width(p->E, p->Ev, kernel_score(p), p->mask, p->diff)) return FLB200_E_UNSUPPORTED;
   if (p->L > (1 << 24) || p->S > (1 << 24)) return FLB200_E_UNSUPPORTED;
   {
     const int H = p->diff ? p->Hq / 2 : p->Hq;
     const int rows = p->diff ? kTileM : 2 * kTileM;
-    const int64_t ctas = static_cast<int64_t>((p->L + rows - 1) / rows) * p->N * H;
+    const int64_t ctas = static_cast<int64_t>((p->L + rows - 1) / rows) * p->N * H * (p->diff ? 2 : 1);
     if (ctas > 0x7fffffffLL) return FLB200_E_UNSUPPORTED;
   }
 
@@ -166,8 +183,8 @@ int validate(const flb200_attn_params* p) {
         !mult8(p->o_stride[i]))
       return FLB200_E_MISALIGNED;
   }
-  if (p->q_stride[2] < p->E || p->k_stride[2] < p->E || p->v_stride[2] < p->Ev ||
-      p->o_stride[2] < p->Ev)
+  if (p->q_stride[2] < p->E || p->k_stride[2] < (p->k_keys_contiguous ? p->S : p->E) ||
+      p->v_stride[2] < p->Ev || p->o_stride[2] < p->Ev)
     return FLB200_E_BAD_ARG;
   if (p->score_mod == FLB200_SCORE_BIAS) {
     for (int b = 0; b < 2; ++b) {
@@ -190,7 +207,7 @@ int validate(const flb200_attn_params* p) {
 // other's tiles: document masks, additive biases (Evoformer rows), and launches too small to give
 // every SM two-stage work.  FLB200_STAGES=1|2 overrides the choice for tuning.
 int pick_stages(const flb200_attn_params* p) {
-  if (p->diff) return 2;
+  if (p->diff || p->product_chain) return 2;
   if (const char* e = std::getenv("FLB200_STAGES")) {
     const int v = std::atoi(e);
     if (v == 1 || v == 2) return v;
@@ -230,10 +247,10 @@ int build_block_map(const flb200_attn_params* p, cudaStream_t stream) {
 template <int E, int EV, bool DIFF, int STAGES>
 cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUtensorMap& b,
                           const CUtensorMap& c, const CUtensorMap& o, const KernelParams& kp,
-                          int grid, cudaStream_t st) {
+                          int grid, int cluster, cudaStream_t st) {
 #define FLB_CASE(SC, MK)          \
   if (score == SC && mask == MK)  \
-    return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, kp, grid, st);
+    return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, kp, grid, cluster, st);
   if constexpr (DIFF) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
@@ -241,6 +258,10 @@ cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUten
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
     FLB_CASE(SCORE_BIAS, MASK_NONE)
+    if constexpr (STAGES == 2) {
+      FLB_CASE(SCORE_B2B, MASK_NONE)
+      FLB_CASE(SCORE_B2BT, MASK_NONE)
+    }
   } else {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
@@ -252,6 +273,10 @@ cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUten
     FLB_CASE(SCORE_NONE, MASK_PREFIX)
     FLB_CASE(SCORE_NONE, MASK_DOCUMENT)
     FLB_CASE(SCORE_BIAS, MASK_NONE)
+    if constexpr (STAGES == 2) {
+      FLB_CASE(SCORE_B2B, MASK_NONE)
+      FLB_CASE(SCORE_B2BT, MASK_NONE)
+    }
   }
 #undef FLB_CASE
   return cudaErrorInvalidValue;
@@ -337,6 +362,7 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
   kp.alibi_log2_slope_step = p->score_mod == FLB200_SCORE_ALIBI ? -8.0f / p->alibi_heads : 0.f;
   kp.alibi_head0 = p->alibi_head0;
   kp.softcap = p->softcap;
+  kp.pointwise = p->pointwise;
   kp.lse = p->lse;
   kp.lse_sn = p->lse_stride[0];
   kp.lse_sh = p->lse_stride[1];
@@ -381,16 +407,26 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
   }
 
   // tensor maps: innermost feature axis, then row, head, batch
-  const int width = kernel_width(p->E, p->Ev, p->score_mod, p->mask, p->diff);  // q/k width
-  const int vwidth = p->diff ? 2 * width : width;
+  const int kscore = kernel_score(p);
+  const int width = kernel_width(p->E, p->Ev, kscore, p->mask, p->diff);  // q/k width
+  // value columns one CTA handles: twice the q/k width for the differential kernels, except the
+  // widest, whose CTAs come in pairs that split value heads above 128
+  const int vwidth = p->diff ? (width == 128 ? 128 : 2 * width) : width;
+  kp.v_halves = (p->diff && width == 128 && p->Ev > 128) ? 2 : 1;
+  kp.v_exchange = kp.v_halves == 2 && p->diff_rms_norm;
+  kp.inv_ev = 1.0f / static_cast<float>(p->Ev);
   const uint32_t kbox = width >= 64 ? 64 : width;
   const uint32_t vbox = vwidth >= 64 ? 64 : vwidth;
   const int Hv = p->diff ? H : p->Hkv;
   CUtensorMap tmQ, tmK, tmV, tmO;
   if (make_tmap_bf16_4d(&tmQ, p->q, p->E, p->L, p->Hq, p->N, p->q_stride[2], p->q_stride[1],
                         p->q_stride[0], kbox, kTileM) ||
-      make_tmap_bf16_4d(&tmK, p->k, p->E, p->S, p->Hkv, p->N, p->k_stride[2], p->k_stride[1],
-                        p->k_stride[0], kbox, kTileN) ||
+      (p->k_keys_contiguous
+           // K^T: keys innermost, one box = 64 keys x all feature rows
+           ? make_tmap_bf16_4d(&tmK, p->k, p->S, p->E, p->Hkv, p->N, p->k_stride[2], p->k_stride[1],
+                               p->k_stride[0], 64, width)
+           : make_tmap_bf16_4d(&tmK, p->k, p->E, p->S, p->Hkv, p->N, p->k_stride[2], p->k_stride[1],
+                               p->k_stride[0], kbox, kTileN)) ||
       make_tmap_bf16_4d(&tmV, p->v, p->Ev, p->S, Hv, p->N, p->v_stride[2], p->v_stride[1],
                         p->v_stride[0], vbox, kTileN) ||
       make_tmap_bf16_4d(&tmO, p->o, p->Ev, p->L, H, p->N, p->o_stride[2], p->o_stride[1],
@@ -419,20 +455,22 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
       if (sec < bh_count) kp.sec_bh = static_cast<int>(sec);
     }
   }
-  const int grid = kp.nq_blocks * p->N * H;
+  const int grid = kp.nq_blocks * p->N * H * kp.v_halves;
+  const int cluster = kp.v_exchange ? 2 : 1;
   cudaError_t e = cudaErrorInvalidValue;
-  const int sc = p->score_mod, mk = p->mask;
+  const int sc = kscore, mk = p->mask;
   if (p->diff) {
-    if (width == 64) e = dispatch_mods<64, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else e = dispatch_mods<32, 64, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    if (width == 128) e = dispatch_mods<128, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 64) e = dispatch_mods<64, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else e = dispatch_mods<32, 64, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   } else if (stages == 2) {
-    if (width == 128) e = dispatch_mods<128, 128, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else if (width == 64) e = dispatch_mods<64, 64, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else e = dispatch_mods<32, 32, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    if (width == 128) e = dispatch_mods<128, 128, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else e = dispatch_mods<32, 32, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   } else {
-    if (width == 128) e = dispatch_mods<128, 128, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else if (width == 64) e = dispatch_mods<64, 64, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
-    else e = dispatch_mods<32, 32, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, stream);
+    if (width == 128) e = dispatch_mods<128, 128, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else e = dispatch_mods<32, 32, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   }
   if (e != cudaSuccess) return FLB200_E_LAUNCH;
   g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -108,6 +108,60 @@ FLB_DEV bool mbar_wait(uint32_t bar, uint32_t parity, WaitCtl* ctl) {
 }
 
 // ----------------------------------------------------------------------------
+// thread-block clusters: plain distributed-shared-memory stores and remote barrier arrivals
+// (no multicast form of any load is used anywhere in this library)
+// ----------------------------------------------------------------------------
+FLB_DEV uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// address of `local_smem_addr` in the shared memory of CTA `rank` of this cluster
+FLB_DEV uint32_t cluster_map(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_smem_addr), "r"(rank));
+  return a;
+}
+FLB_DEV void cluster_store_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+FLB_DEV void cluster_mbar_arrive(uint32_t cluster_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+// every thread of every CTA of the cluster arrives and waits (hardware barrier)
+FLB_DEV void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+FLB_DEV bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier that a thread of another CTA of the cluster arrives at.
+FLB_DEV bool mbar_wait_cluster(uint32_t bar, uint32_t parity, WaitCtl* ctl) {
+  const uint64_t t0 = globaltimer_ns();
+  const uint64_t limit_ns = static_cast<uint64_t>(ctl->limit_us) * 1000ull;
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (ctl->abort) return false;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      ctl->abort = 1;
+      return false;
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), per-CTA loads only
 // ----------------------------------------------------------------------------
 FLB_DEV void tma_prefetch_desc(const void* tmap) {
@@ -199,6 +253,20 @@ FLB_DEV void umma_ss_c(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t
       "mov.b64 db, {%2, %3};\n\t"
       "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
       ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "n"(ACC), "r"(leader)
+      : "memory");
+}
+// as umma_ss_c, with separate high descriptor words for the two operands (different layouts)
+template <int ACC>
+FLB_DEV void umma_ss2_c(uint32_t leader, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                        uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(ACC), "r"(leader)
       : "memory");
 }
 template <int ACC>

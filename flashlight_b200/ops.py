@@ -260,5 +260,69 @@ def _attn_fwd_fake(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap,
     return q.new_empty((N, Ho, L, Ev))
 
 
+_POINTWISE = {"identity": _lib.PW_IDENTITY, "relu": _lib.PW_RELU, "tanh": _lib.PW_TANH, "sigmoid": _lib.PW_SIGMOID}
+
+
+@torch.library.custom_op("flb200::product_chain", mutates_args=())
+def product_chain(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, scale: float, pointwise: str) -> torch.Tensor:
+    """f((a @ b) * scale) @ c in one kernel, no softmax: a [B, M, N], b [B, N, O], c [B, O, P] bf16 with
+    N, P <= 128 -> [B, M, P].  The counterpart of the reference's fused `bmm(f(bmm(a, b)), c)`
+    template (monkeypatch/template/fused_bmm.py:332-422).  `b` is read where it lies: with its last
+    axis contiguous (the natural [B, N, O] layout) or as a transposed view of a [B, O, N] tensor."""
+    lib = _lib.load()
+    if pointwise not in _POINTWISE:
+        raise NotImplementedError(f"flb200: pointwise must be one of {sorted(_POINTWISE)}")
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise RuntimeError("flb200: tensors must live on a CUDA device (there is no CPU path)")
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or c.dtype != torch.bfloat16:
+        raise NotImplementedError("flb200: only bfloat16 inputs are supported")
+    if a.dim() != 3 or b.dim() != 3 or c.dim() != 3:
+        raise ValueError("flb200: a, b, c must be 3-D [batch, rows, cols]")
+    B, M, N = a.shape
+    O, P = c.size(1), c.size(2)
+    if b.shape != (B, N, O) or c.size(0) != B:
+        raise ValueError("flb200: inconsistent shapes for (a @ b) @ c")
+    if a.stride(2) != 1:
+        a = a.contiguous()
+    if c.stride(2) != 1:
+        c = c.contiguous()
+    keys_contiguous = b.stride(2) == 1
+    if not keys_contiguous and b.stride(1) != 1:
+        b = b.contiguous()
+        keys_contiguous = True
+    if keys_contiguous and b.stride(1) % 8 != 0 and N % 8 == 0:
+        # rows of O keys that do not start on 16-byte boundaries cannot be fetched as tiles: lay b
+        # out as O rows of N features instead
+        b = b.transpose(1, 2).contiguous().transpose(1, 2)
+        keys_contiguous = False
+    o = torch.empty((B, M, P), dtype=a.dtype, device=a.device)
+    p = _lib.new_params()
+    p.product_chain, p.pointwise, p.k_keys_contiguous = 1, _POINTWISE[pointwise], int(keys_contiguous)
+    p.N, p.Hq, p.Hkv, p.L, p.S, p.E, p.Ev = B, 1, 1, M, O, N, P
+    p.q, p.k, p.v, p.o = a.data_ptr(), b.data_ptr(), c.data_ptr(), o.data_ptr()
+    p.q_stride[0], p.q_stride[1], p.q_stride[2] = a.stride(0), 0, a.stride(1)
+    # k: rows of features [O][N] (b given as a transposed view), or feature rows of keys [N][O]
+    p.k_stride[0], p.k_stride[1] = b.stride(0), 0
+    p.k_stride[2] = b.stride(1) if keys_contiguous else b.stride(2)
+    p.v_stride[0], p.v_stride[1], p.v_stride[2] = c.stride(0), 0, c.stride(1)
+    p.o_stride[0], p.o_stride[1], p.o_stride[2] = o.stride(0), 0, o.stride(1)
+    p.scale = float(scale)
+    p.status = _status_word(a.device).data_ptr()
+    mirror = _status_mirror(a.device)
+    if int(mirror[0]) != 0:
+        check_status(a.device)
+    p.status_host = mirror.data_ptr()
+    with torch.cuda.device(a.device):
+        rc = lib.flb200_attn_fwd(C.byref(p), C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
+    if rc != _lib.OK:
+        _raise_for(rc, "product_chain")
+    return o
+
+
+@product_chain.register_fake
+def _product_chain_fake(a, b, c, scale, pointwise):
+    return a.new_empty((a.size(0), a.size(1), c.size(2)))
+
+
 def clear_block_map_cache() -> None:
     _MAP_CACHE.clear()

@@ -63,6 +63,14 @@ typedef enum flb200_score_mod {
   FLB200_SCORE_BIAS = 3     /* s + bias[0] + bias[1]                       evoformer.py:24-27 */
 } flb200_score_mod;
 
+/* Pointwise function between the two products of a product chain. */
+typedef enum flb200_pointwise {
+  FLB200_PW_IDENTITY = 0,
+  FLB200_PW_RELU = 1,
+  FLB200_PW_TANH = 2,
+  FLB200_PW_SIGMOID = 3
+} flb200_pointwise;
+
 /* Mask; masked pairs get weight zero.  i = query index, j = key index. */
 typedef enum flb200_mask {
   FLB200_MASK_NONE = 0,
@@ -162,6 +170,16 @@ typedef struct flb200_attn_params {
    * formula (head h of the call uses slope index alibi_head0 + h).  0 unless the heads of one
    * model are split over several calls. */
   int32_t alibi_head0;
+
+  /* Back-to-back matrix product without softmax (monkeypatch/template/fused_bmm.py:332-422 of the
+   * reference: `(f(A @ B)) @ C` with a pointwise middle).  With product_chain != 0 the call
+   * computes o = f(q k^T * scale) v:  A = q [N][H][M=L][N=E], C = v [N][H][O=S][P=Ev], and B is k,
+   * either as rows of features [N][H][S][E] (k_keys_contiguous = 0) or, as the reference's B
+   * operand lies in memory, [N][H][E][S] with the keys contiguous (k_keys_contiguous = 1; k_stride
+   * is then {batch, head, feature row}).  score_mod and mask must be NONE, diff 0, lse NULL. */
+  int32_t product_chain;
+  int32_t pointwise;          /* flb200_pointwise */
+  int32_t k_keys_contiguous;
 } flb200_attn_params;
 
 /* ABI version of the loaded library (FLB200_ABI_VERSION it was built with). */

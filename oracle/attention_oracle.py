@@ -249,3 +249,14 @@ def evoformer(q_input, k_input, v_input, biases: Sequence[torch.Tensor], sm_scal
 
     out = _attend(q, k, v, _scale(q, sm_scale), score_mod=mod, dtype=dtype, **kw)
     return out.transpose(1, 2).reshape(*lead, S, H, out.size(-1))
+
+
+def product_chain(a, b, c, pointwise: str = "identity", scale: float = 1.0, dtype=torch.float32):
+    """(f((a @ b) * scale)) @ c with the intermediate rounded to bf16 before the second product, as the
+    reference's fused template does (monkeypatch/template/fused_bmm.py:398-404: `acc_ab` through the
+    pointwise subgraph, `.to(c.type.element_ty)`, second `tl.dot`); its own test is the identity case
+    `torch.bmm(torch.bmm(a, b), c)` (fused_bmm.py:433-434).  Both products accumulate in `dtype`."""
+    f = {"identity": lambda x: x, "relu": torch.relu, "tanh": torch.tanh, "sigmoid": torch.sigmoid}[pointwise]
+    mid = f(torch.matmul(a.to(dtype), b.to(dtype)) * scale)
+    mid = mid.to(torch.bfloat16).to(dtype)
+    return torch.matmul(mid, c.to(dtype))

@@ -93,6 +93,12 @@ def main(ref_root: str) -> None:
     cases["evoformer_mask"] = dict(q=q, k=k, v=v, bias1=bm, bias2=b2,
                                    out=evoformer.attention_reference(*f32(q, k, v), [bm.float(), b2.float()]))
 
+    # differential attention at q/k width 128, value width 256: the reference's own test shape family
+    # (tests/test_diffattn.py:25-34); drawn after every other case so that those keep their values
+    q, k = rnd(g, 1, 4, 200, 128), rnd(g, 1, 4, 200, 128)
+    v = rnd(g, 1, 2, 200, 256)
+    cases["diff_d128"] = dict(q=q, k=k, v=v, lam=0.2, out=diff_attn.diffattn(*f32(q, k, v)))
+
     for name, c in cases.items():
         c["out"] = c["out"].contiguous()
         torch.save(c, HERE / f"{name}.pt")

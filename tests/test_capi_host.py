@@ -112,7 +112,12 @@ def test_diff_shapes(lib):
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
     p = good(diff=1, E=64, Ev=128, Hq=8, Hkv=4)
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.E_BAD_ARG
-    p = good(diff=1, E=128, Ev=512, Hq=8, Hkv=8)
+    p = good(diff=1, E=128, Ev=256, Hq=8, Hkv=8)   # the reference's d=128 test shape: two CTAs per item
+    for name, w in (("v_stride", 256), ("o_stride", 256)):
+        arr = getattr(p, name)
+        arr[2], arr[1], arr[0] = w, w * 256, w * 256 * 4
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
+    p.Ev = 512
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.E_UNSUPPORTED
 
 

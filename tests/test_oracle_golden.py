@@ -71,7 +71,7 @@ def test_prefix():
     close(ao.prefix_lm(c["q"], c["k"], c["v"], prefix_lengths=pl), c["out"])
 
 
-@pytest.mark.parametrize("name", ["diff", "diff_l08"])
+@pytest.mark.parametrize("name", ["diff", "diff_l08", "diff_d128"])
 def test_diff(name):
     c = load(name)
     close(ao.diffattn(c["q"], c["k"], c["v"], lambda_full=c["lam"]), c["out"])

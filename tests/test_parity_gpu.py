@@ -84,7 +84,7 @@ def test_golden_prefix(stages):
     check(av.attention_pytorch_prefix_lm(c["q"], c["k"], c["v"], prefix_lengths=c["prefix"]), c["out"])
 
 
-@pytest.mark.parametrize("name", ["diff", "diff_l08"])
+@pytest.mark.parametrize("name", ["diff", "diff_l08", "diff_d128"])
 def test_golden_diff(name):
     c = load(name)
     check(av.diffattn(c["q"], c["k"], c["v"], lambda_full=c["lam"]), c["out"])
@@ -389,3 +389,31 @@ def test_vanilla_workload_against_cpu_oracle():
     ref = run_oracle(w, t)                                   # fp32 on the host, as configured
     out = run_product(w, {k: v.cuda() for k, v in t.items()})
     check(out, ref)
+
+
+# ---------------------------------------------------------------- differential attention, wide heads
+@pytest.mark.parametrize("S", [128, 700])
+@pytest.mark.parametrize("d", [128, 96])
+def test_diff_attention_with_value_heads_of_256(d, S):
+    """q/k heads of 128 with value heads of 256, the reference's own test shape family
+    (tests/test_diffattn.py:25-34: B16 H16 S1024 d128): two CTAs per work item take one half of the
+    value columns each; with the RMS normalisation they run as a cluster and swap row sums."""
+    q, k = rnd((2, 4, S, d), 80), rnd((2, 4, S, d), 81)
+    v = rnd((2, 2, S, 2 * d), 82)
+    check(av.diffattn(q, k, v), ao.diffattn(q, k, v))
+    check(av.diffattn(q, k, v, lambda_full=0.8, is_causal=True), ao.diffattn(q, k, v, lambda_full=0.8, is_causal=True))
+    check(av.diffattn(q, k, v, lambda_full=0.8, is_causal=True, rms_norm=True, rms_eps=1e-5),
+          ao.diffattn(q, k, v, lambda_full=0.8, is_causal=True, rms_norm=True, rms_eps=1e-5))
+
+
+def test_diff_attention_reference_test_shape():
+    q, k = rnd((16, 16, 1024, 128), 83), rnd((16, 16, 1024, 128), 84)
+    v = rnd((16, 8, 1024, 256), 85)
+    out = av.diffattn(q, k, v)
+    ref = torch.cat([ao.diffattn(q[n:n + 4], k[n:n + 4], v[n:n + 4]) for n in range(0, 16, 4)])
+    check(out, ref)
+
+
+def test_diff_rms_norm_divides_by_the_true_width():
+    q, k, v = rnd((1, 4, 300, 48), 86), rnd((1, 4, 300, 48), 87), rnd((1, 2, 300, 96), 88)
+    check(av.diffattn(q, k, v, lambda_full=0.5, rms_norm=True), ao.diffattn(q, k, v, lambda_full=0.5, rms_norm=True))
