@@ -4,8 +4,8 @@ H = dim // D, FLOPs counted as twice a vanilla attention (8 * B * S^2 * H * D).
 
     python -m flashlight_b200.benchmarks.run_diff_attn --output diff_attn
 
-Head dimension 128 needs a 256-wide V accumulator per stage, which does not fit this kernel's
-tensor-memory layout; such rows are reported as `nan` instead of being computed some other way.
+Head dimension 128 (value heads of 256) runs as pairs of CTAs that take one half of the value
+columns each.  A shape without a kernel would be reported as `nan`, never computed some other way.
 """
 from __future__ import annotations
 

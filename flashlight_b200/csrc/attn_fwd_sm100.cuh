@@ -66,6 +66,12 @@ struct AttnCfg {
 #endif
   static constexpr bool EARLY_PV = FLB_SOFTCAP_EARLY_PV && SCORE_ == SCORE_SOFTCAP;
   // back-to-back product O = f(Q K^T * scale) V: no softmax; KT: K arrives as [E][S], keys contiguous
+  // Resident pair bias: the CTA keeps one (head, query tile), loads that tile's pair-bias columns
+  // once and walks a range of rows (MSA rows of Evoformer attention) that all add the same bias;
+  // the two stages work on two rows at a time, each with its own Q, K and V.
+  static constexpr bool ROWLOOP = SCORE_ == SCORE_BIAS_RES;
+  static constexpr bool BIAS = SCORE_ == SCORE_BIAS || ROWLOOP;
+  static_assert(!ROWLOOP || (STAGES_ == 2 && !DIFF_ && EV_ <= 64 && E_ <= 64), "resident bias: narrow heads, two stages");
   static constexpr bool B2B = SCORE_ == SCORE_B2B || SCORE_ == SCORE_B2BT;
   static constexpr bool KT = SCORE_ == SCORE_B2BT;
   static constexpr int KBOX = E >= 64 ? 64 : E;     // elements per swizzled row of a Q/K box
@@ -75,14 +81,21 @@ struct AttnCfg {
   static constexpr int V_BOX_BYTES = 128 * VBOX * 2;
   static constexpr int Q_BYTES = 128 * E * 2;                    // one stage
   static constexpr int K_HEAD_BYTES = 128 * E * 2;               // one head's K tile
-  static constexpr int K_BYTES = K_HEAD_BYTES * (DIFF ? 2 : 1);  // diff: two heads side by side
-  static constexpr int V_BYTES = 128 * EV * 2;
+  // diff: two heads' K side by side; resident bias: the two stages' (rows') K and V side by side
+  static constexpr int K_BYTES = K_HEAD_BYTES * ((DIFF || ROWLOOP) ? 2 : 1);
+  static constexpr int V_HEAD_BYTES = 128 * EV * 2;
+  static constexpr int V_BYTES = V_HEAD_BYTES * (ROWLOOP ? 2 : 1);
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
   static constexpr int SMEM_BUDGET = STAGES == 2 ? 224 * 1024 : 110 * 1024;
   static constexpr int NSTAGE_FIT = (SMEM_BUDGET - STAGES * Q_BYTES) / SLOT_BYTES;
-  static constexpr int NSTAGE = NSTAGE_FIT > 8 ? 8 : NSTAGE_FIT;
+  // Resident bias: everything between the Q tiles / output staging and the barriers is shared by
+  // the K/V ring and the bias tiles; the launch decides the split (KernelParams::res_slots): the
+  // bias takes 32 KB per key tile, the ring what is left, at least two slots and at most seven.
+  static constexpr int NSTAGE = ROWLOOP ? 7 : (NSTAGE_FIT > 8 ? 8 : NSTAGE_FIT);
   static constexpr int AUX_BYTES = 2048;
-  static constexpr int SMEM_USED = 1024 + STAGES * Q_BYTES + NSTAGE * SLOT_BYTES + AUX_BYTES;
+  // output staging of its own (the Q tiles are reloaded for the next rows while a result is stored)
+  static constexpr int OSTAGE_BYTES = ROWLOOP ? 2 * V_HEAD_BYTES : 0;
+  static constexpr int SMEM_USED = ROWLOOP ? 232448 : 1024 + STAGES * Q_BYTES + NSTAGE * SLOT_BYTES + AUX_BYTES;
   // Shared memory also bounds how many CTAs share an SM, and with it their tensor-memory demand
   // (an allocation that does not fit would wait for a neighbour to leave): two-stage CTAs take
   // more than half of it (512 columns each), one-stage CTAs more than a third (256 columns each).
@@ -128,7 +141,11 @@ enum : int {
   BAR_KV_FULL = 14,    // +slot
   BAR_KV_EMPTY = 22,   // +slot
   BAR_S_FREE = 30,     // +s   softmax -> MMA: S tile read into registers (only with SEP_P)
-  BAR_COUNT = 32
+  BAR_COUNT = 32,
+  // resident-bias kernel (uses neither P_HALF nor O_STAGED, and at most four K/V slots)
+  BAR_Q_EMPTY = BAR_P_HALF,    // +s   MMA -> producer: the row's last QK product has read Q
+  BAR_O_FREE = BAR_O_STAGED,   // +s   epilogue -> MMA / softmax: the row's accumulator and row sums are read
+  BAR_BIAS_FULL = 21           //      producer -> softmax: the pair-bias tiles are in shared memory
 };
 
 struct TileRange {
@@ -189,8 +206,13 @@ template <class C>
 struct Smem {
   uint8_t* base;
   FLB_DEV uint8_t* q(int s) const { return base + s * C::Q_BYTES; }
-  FLB_DEV uint8_t* slot(int i) const { return base + C::STAGES * C::Q_BYTES + i * C::SLOT_BYTES; }
-  FLB_DEV uint8_t* aux() const { return base + C::STAGES * C::Q_BYTES + C::NSTAGE * C::SLOT_BYTES; }
+  FLB_DEV uint8_t* ostage(int s) const { return base + C::STAGES * C::Q_BYTES + s * C::V_HEAD_BYTES; }
+  FLB_DEV uint8_t* slot(int i) const {
+    return base + C::STAGES * C::Q_BYTES + C::OSTAGE_BYTES + i * C::SLOT_BYTES;
+  }
+  // resident bias tiles: behind the `slots` K/V slots this launch uses
+  FLB_DEV uint8_t* bias(int slots) const { return slot(slots); }
+  FLB_DEV uint8_t* aux() const { return base + (C::SMEM_USED - 1024 - C::AUX_BYTES); }
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
   FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }
   FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
@@ -282,6 +304,78 @@ FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensor
   }
 }
 
+// Rows a resident-bias CTA walks: `count` rows from batch index n0 on, stage s taking the rows
+// n0 + s, n0 + s + 2, ...; every row spans nt key tiles.
+struct RowWalk {
+  int n0, count, nt;
+  FLB_DEV int items(int s) const { return (count + 1 - s) >> 1; }
+};
+
+// Producer of the resident-bias kernel: the pair-bias tiles of this (head, query tile) once, then
+// per pair of rows their Q tiles and, tile by tile, both rows' K and V side by side in one slot.
+template <class C>
+FLB_DEV void load_role_rows(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensorMap* tmK,
+                            const CUtensorMap* tmV, const CUtensorMap* tmB, const KernelParams& p,
+                            int b, int h, int r0, RowWalk rw) {
+  if (p.withhold_loads) return;
+  mbar_arrive_expect_tx(sm.bar(BAR_BIAS_FULL), rw.nt * 32768);
+#pragma unroll 1
+  for (int t = 0; t < rw.nt; ++t)
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb)
+      tma_load_4d(smem_u32(sm.bias(p.res_slots)) + (t * 2 + kb) * 16384, tmB, sm.bar(BAR_BIAS_FULL),
+                  t * kTileN + kb * 64, r0, h * p.pair_h, b * p.pair_b);
+  int slot = 0;
+  uint32_t ph = 0;  // ring position of the next load and how often the ring has wrapped (parity)
+  const int pairs = rw.items(0);
+#pragma unroll 1
+  for (int item = 0; item < pairs; ++item) {
+    const int live = item < rw.items(1) ? 2 : 1;  // the last pair of an odd count has one row
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (s < live) {
+        // the Q tile is free once the previous row's last QK product has read it
+        if (item > 0) FLB_WAIT(sm, BAR_Q_EMPTY + s, (item - 1) & 1);
+        mbar_arrive_expect_tx(sm.bar(BAR_Q_FULL + s), C::Q_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < C::NKB; ++kb)
+          tma_load_4d(smem_u32(sm.q(s)) + kb * C::QK_BOX_BYTES, tmQ, sm.bar(BAR_Q_FULL + s),
+                      kb * C::KBOX, r0, h, rw.n0 + 2 * item + s);
+      }
+    }
+#pragma unroll 1
+    for (int t = 0; t < rw.nt; ++t) {
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {  // K(t) of both rows, then V(t) of both rows
+        FLB_WAIT(sm, BAR_KV_EMPTY + slot, ph ^ 1);
+        mbar_arrive_expect_tx(sm.bar(BAR_KV_FULL + slot), live * (kv ? C::V_HEAD_BYTES : C::K_HEAD_BYTES));
+        const uint32_t dst = smem_u32(sm.slot(slot));
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (s < live) {
+            const int n = rw.n0 + 2 * item + s;
+            if (kv == 0) {
+#pragma unroll
+              for (int kb = 0; kb < C::NKB; ++kb)
+                tma_load_4d(dst + s * C::K_HEAD_BYTES + kb * C::QK_BOX_BYTES, tmK,
+                            sm.bar(BAR_KV_FULL + slot), kb * C::KBOX, t * kTileN, h, n);
+            } else {
+#pragma unroll
+              for (int vb = 0; vb < C::NVB; ++vb)
+                tma_load_4d(dst + s * C::V_HEAD_BYTES + vb * C::V_BOX_BYTES, tmV,
+                            sm.bar(BAR_KV_FULL + slot), vb * C::VBOX, t * kTileN, h, n);
+            }
+          }
+        }
+        if (++slot == p.res_slots) {
+          slot = 0;
+          ph ^= 1;
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // MMA issue (one warp, one issuing lane).  Order per step t:  PV0(t-1) QK0(t) PV1(t-1) QK1(t).  The tensor core
 // executes in issue order, which keeps the two stages half a period apart: while one stage's
@@ -291,7 +385,7 @@ FLB_DEV void load_role(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensor
 // ------------------------------------------------------------------------------------------
 template <class C>
 FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
-                      const TileRange (&rg)[2], int lo, int hi) {
+                      const TileRange (&rg)[2], int lo, int hi, [[maybe_unused]] int row_tiles = 0) {
   const uint32_t leader = elect_one() ? 1u : 0u;  // the lane that issues; all lanes run the loop
   constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, C::KT ? 1 : 0);
   constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
@@ -319,6 +413,11 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                             k_lo0 + ((smem_u32(sm.q(1)) & 0x3FFFFu) >> 4)};
   const uint32_t slot0 = (smem_u32(sm.slot(0)) & 0x3FFFFu) >> 4;
   bool q_ready[2] = {false, false};
+  // resident-bias kernel: the walk strings the rows' tiles together (`row_tiles` per row); tile
+  // index inside the row and row index of the next PV and QK product of each stage
+  [[maybe_unused]] int pv_t[2] = {0, 0}, pv_row[2] = {0, 0}, qk_t[2] = {0, 0}, qk_row[2] = {0, 0};
+  [[maybe_unused]] int ring_slot = 0;
+  [[maybe_unused]] uint32_t ring_ph = 0;
 
   // position u of the walk holds tile lo + u (or hi - 1 - u when the walk is reversed); stage s
   // takes part in positions [first[s], first[s] + cnt[s])
@@ -329,12 +428,33 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
 #pragma unroll 1
   for (int u = 0; u <= n_pos; ++u) {
     const bool have_k = u < n_pos, have_v = u > 0;
-    const int kseq = 2 * u, vseq = 2 * (u - 1) + 1;
-    const int kslot = kseq % C::NSTAGE, vslot = have_v ? vseq % C::NSTAGE : 0;
+    int kslot, vslot;
+    uint32_t kph, vph;
+    if constexpr (C::ROWLOOP) {
+      // ring of p.res_slots slots, taken in load order: V(u - 1), then K(u)
+      vslot = ring_slot;
+      vph = ring_ph;
+      if (have_v && ++ring_slot == p.res_slots) {
+        ring_slot = 0;
+        ring_ph ^= 1;
+      }
+      kslot = ring_slot;
+      kph = ring_ph;
+      if (have_k && ++ring_slot == p.res_slots) {
+        ring_slot = 0;
+        ring_ph ^= 1;
+      }
+    } else {
+      const int kseq = 2 * u, vseq = 2 * (u - 1) + 1;
+      kslot = kseq % C::NSTAGE;
+      vslot = have_v ? vseq % C::NSTAGE : 0;
+      kph = (kseq / C::NSTAGE) & 1;
+      vph = (vseq / C::NSTAGE) & 1;
+    }
     const uint32_t v_lo = v_lo0 + slot0 + vslot * (C::SLOT_BYTES >> 4);
     const uint32_t k_lo = k_lo0 + slot0 + kslot * (C::SLOT_BYTES >> 4);
-    if (have_v) FLB_WAIT(sm, BAR_KV_FULL + vslot, (vseq / C::NSTAGE) & 1);
-    if (have_k) FLB_WAIT(sm, BAR_KV_FULL + kslot, (kseq / C::NSTAGE) & 1);
+    if (have_v) FLB_WAIT(sm, BAR_KV_FULL + vslot, vph);
+    if (have_k) FLB_WAIT(sm, BAR_KV_FULL + kslot, kph);
 #pragma unroll
     for (int s = 0; s < C::STAGES; ++s) {
       // With P in columns of its own the scores of the next tile go first (they only wait for S to
@@ -345,7 +465,18 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
           // O_s += P_s(t-1) V(t-1)
           if (have_v && u - 1 >= first[s] && u - 1 < first[s] + cnt[s]) {
             const int it = u - 1 - first[s];
+            bool fresh = it == 0;  // first product of a row: the accumulator is overwritten
+            if constexpr (C::ROWLOOP) {
+              fresh = pv_t[s] == 0;
+              // ... which the epilogue must have read for the previous row
+              if (fresh && pv_row[s] > 0) FLB_WAIT(sm, BAR_O_FREE + s, (pv_row[s] - 1) & 1);
+              if (++pv_t[s] == row_tiles) {
+                pv_t[s] = 0;
+                ++pv_row[s];
+              }
+            }
             const uint32_t tA = C::SEP_P ? tP[s] : tS[s];  // where the softmax warps put P
+            const uint32_t vs_lo = v_lo + (C::ROWLOOP ? s * (C::V_HEAD_BYTES >> 4) : 0);
             // the product starts on the first 64 keys while the softmax warps finish the rest
             if constexpr (C::EARLY_PV) {
               FLB_WAIT(sm, BAR_P_HALF + s, it & 1);
@@ -353,15 +484,15 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
               FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
             }
             tc_fence_after();
-            if (it > 0) umma_ts_c<1>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
-            else umma_ts_c<0>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
+            if (!fresh) umma_ts_c<1>(leader, tO[s], tA, vs_lo, v_hi, idesc_pv);
+            else umma_ts_c<0>(leader, tO[s], tA, vs_lo, v_hi, idesc_pv);
 #pragma unroll
             for (int k = 1; k < kTileN / 32; ++k)
-              umma_ts_c<1>(leader, tO[s], tA + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
+              umma_ts_c<1>(leader, tO[s], tA + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
             if constexpr (C::SPLIT_P) {
 #pragma unroll
               for (int k = 0; k < kTileN / 32; ++k)
-                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
+                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
                              idesc_pv);
             }
             if constexpr (C::EARLY_PV) {
@@ -370,11 +501,11 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
             }
 #pragma unroll
             for (int k = kTileN / 32; k < kTileN / 16; ++k)
-              umma_ts_c<1>(leader, tO[s], tA + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
+              umma_ts_c<1>(leader, tO[s], tA + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
             if constexpr (C::SPLIT_P) {
 #pragma unroll
               for (int k = kTileN / 32; k < kTileN / 16; ++k)
-                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
+                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
                              idesc_pv);
             }
             umma_commit_c(leader, sm.bar(BAR_PV_DONE + s));
@@ -382,7 +513,12 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
         } else {
           // S_s = Q_s K(t)^T
           if (have_k && u >= first[s] && u < first[s] + cnt[s]) {
-            if (!q_ready[s]) {
+            if constexpr (C::ROWLOOP) {
+              if (qk_t[s] == 0) {  // first tile of a row: its Q tile must have landed
+                FLB_WAIT(sm, BAR_Q_FULL + s, qk_row[s] & 1);
+                tc_fence_after();
+              }
+            } else if (!q_ready[s]) {
               FLB_WAIT(sm, BAR_Q_FULL + s, 0);
               q_ready[s] = true;
               tc_fence_after();
@@ -405,7 +541,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                 umma_ss2_c<1>(leader, tS[s], q_lo[s] + off, k_hi, kt_lo + ((kk * 128) >> 4), kt_hi, idesc_qk);
               }
             } else {
-              const uint32_t ks_lo = k_lo + (C::DIFF ? s * (C::K_HEAD_BYTES >> 4) : 0);
+              const uint32_t ks_lo = k_lo + ((C::DIFF || C::ROWLOOP) ? s * (C::K_HEAD_BYTES >> 4) : 0);
               umma_ss_c<0>(leader, tS[s], q_lo[s], ks_lo, k_hi, idesc_qk);
 #pragma unroll
               for (int k = 1; k < C::E / 16; ++k) {
@@ -415,6 +551,13 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
               }
             }
             umma_commit_c(leader, sm.bar(BAR_S_FULL + s));
+            if constexpr (C::ROWLOOP) {
+              if (++qk_t[s] == row_tiles) {  // last tile of the row: its Q tile may be replaced
+                qk_t[s] = 0;
+                ++qk_row[s];
+                umma_commit_c(leader, sm.bar(BAR_Q_EMPTY + s));
+              }
+            }
           }
         }
       }
@@ -484,7 +627,10 @@ FLB_DEV float2 exp2_poly2(float2 x) {
 
 template <class C>
 FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p, int s, int n,
-                          int h, int r0, TileRange rg) {
+                          int h, int r0, TileRange rg, [[maybe_unused]] int row_index = 0) {
+  // resident-bias kernel: this call handles one row of the walk; its tiles continue the count of
+  // the tiles of the stage's earlier rows (barrier phases run on that global count)
+  const int it_base = C::ROWLOOP ? row_index * (rg.hi - rg.lo) : 0;
   const int row = threadIdx.x & 127;
   const int i = r0 + row;  // global query row
   const uint32_t lane_base = static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32u;
@@ -497,14 +643,14 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
   // exp2 argument = v * kmul - m * mdom; for plain scores the softmax scale is folded in here
   const float kmul = C::SCORE == SCORE_NONE      ? p.scale_log2
                      : C::SCORE == SCORE_SOFTCAP ? p.softcap * kLog2e
-                     : C::SCORE == SCORE_BIAS    ? kLog2e
+                     : C::BIAS                   ? kLog2e
                                                  : 1.0f;
   // the running maximum m lives in the domain of the raw scores for plain attention, of
   // tanh(score / cap) for softcap and of the biased score (natural units) for additive biases
   // (log2 units after multiplying by mdom); ALiBi scores are in log2 units already
   const float mdom = C::SCORE == SCORE_NONE ? p.scale_log2
                      : C::SCORE == SCORE_SOFTCAP ? p.softcap * kLog2e
-                     : C::SCORE == SCORE_BIAS ? kLog2e : 1.0f;
+                     : C::BIAS ? kLog2e : 1.0f;
 
   float slope2 = 0.f;
   if constexpr (C::SCORE == SCORE_ALIBI) {
@@ -520,6 +666,14 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
       if (p.bias[q])
         brow[q] = reinterpret_cast<const __nv_bfloat16*>(p.bias[q]) + b * p.bias_sb[q] +
                   r * p.bias_sr[q] + h * p.bias_sh[q] + ic * p.bias_sl[q];
+  }
+  if constexpr (C::ROWLOOP) {
+    // the row's key vector (every query row adds the same values), if there is one
+    const int b = n / p.evo_inner, r = n % p.evo_inner;
+    if (p.bias[0])
+      brow[0] = reinterpret_cast<const __nv_bfloat16*>(p.bias[0]) + b * p.bias_sb[0] + r * p.bias_sr[0] +
+                h * p.bias_sh[0];
+    if (row_index == 0) FLB_WAIT(sm, BAR_BIAS_FULL, 0);  // the pair-bias tiles, loaded once
   }
   int pl = 0;
   if constexpr (C::MASK == MASK_PREFIX) pl = prefix_of(p, n);
@@ -549,6 +703,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
   for (int it = 0; it < rg.hi - rg.lo; ++it) {
     const int t = C::REVERSE ? rg.hi - 1 - it : rg.lo + it;
     const int j0 = t * kTileN;
+    const int git = it_base + it;  // tiles of this stage so far
     if constexpr (C::SCORE == SCORE_BIAS) {
       // pull this tile's bias rows (256 B each) into L1 while the scores are still being computed
 #pragma unroll
@@ -561,7 +716,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
           prefetch_l1(last);
         }
     }
-    FLB_WAIT(sm, BAR_S_FULL + s, it & 1);
+    FLB_WAIT(sm, BAR_S_FULL + s, git & 1);
     tc_fence_after();
     uint32_t v[128];
     float m_new = m, m_use = 0.f, sc = 1.0f;
@@ -605,6 +760,43 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
         tmem_ld128_sync(tS, v);
 #pragma unroll
         for (int c = 0; c < 128; ++c) v[c] = f2u(tanh_approx(u2f(v[c]) * inv));
+      }
+    } else if constexpr (C::ROWLOOP) {
+      // s * scale + pair bias (this thread's row of the resident tile: 16 chunks of 8 columns, the
+      // 128-byte rows of each 64-column box swizzled as the tensor map wrote them) + key vector
+      const uint8_t* btile = sm.bias(p.res_slots) + t * 32768 + row * 128;
+      const int sw = row & 7;
+      const float2 mul2 = make_float2(p.scale, p.scale);
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {
+        const uint4 w = *reinterpret_cast<const uint4*>(btile + (c8 >> 3) * 16384 + (((c8 & 7) ^ sw) << 4));
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __ffma2_rn(make_float2(u2f(v[c8 * 8 + 2 * e]), u2f(v[c8 * 8 + 2 * e + 1])), mul2,
+                                      make_float2(u2f(ww[e] << 16), u2f(ww[e] & 0xffff0000u)));
+          v[c8 * 8 + 2 * e] = f2u(x.x);
+          v[c8 * 8 + 2 * e + 1] = f2u(x.y);
+        }
+      }
+      if (brow[0]) {
+        if (j0 + kTileN <= p.S && p.bias_vec[0]) {
+          const uint4* src = reinterpret_cast<const uint4*>(brow[0] + j0);  // same address in every lane
+#pragma unroll
+          for (int c8 = 0; c8 < 16; ++c8) {
+            const uint4 w = __ldg(src + c8);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              v[c8 * 8 + 2 * e] = f2u(u2f(v[c8 * 8 + 2 * e]) + u2f(ww[e] << 16));
+              v[c8 * 8 + 2 * e + 1] = f2u(u2f(v[c8 * 8 + 2 * e + 1]) + u2f(ww[e] & 0xffff0000u));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 128; ++c)
+            v[c] = f2u(u2f(v[c]) + (j0 + c < p.S ? __bfloat162float(brow[0][j0 + c]) : 0.f));
+        }
       }
     } else if constexpr (C::SCORE == SCORE_BIAS) {
       const bool ragged = j0 + kTileN > p.S;
@@ -748,7 +940,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
             // must have been consumed before it is overwritten
             tc_fence_before();
             mbar_arrive(sm.bar(BAR_S_FREE + s));
-            FLB_WAIT(sm, BAR_PV_DONE + s, (it - 1) & 1);
+            FLB_WAIT(sm, BAR_PV_DONE + s, (git - 1) & 1);
           }
 #pragma unroll
           for (int chunk = 0; chunk < 4; ++chunk) tmem_st16(tPs + chunk * 16, pk + chunk * 16);
@@ -794,7 +986,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
     // rescales its 32 rows of O itself.
     sc = (it == 0 || m == -CUDART_INF_F) ? 1.0f : ex2((m - m_use) * mdom);
     if (it == 0 || !__any_sync(0xffffffffu, sc != 1.0f)) break;
-    FLB_WAIT(sm, BAR_PV_DONE + s, (it - 1) & 1);
+    FLB_WAIT(sm, BAR_PV_DONE + s, (git - 1) & 1);
     tc_fence_after();
 #pragma unroll
     for (int c0 = 0; c0 < C::EV; c0 += 32) {
@@ -811,7 +1003,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
       tc_fence_before();
       mbar_arrive(sm.bar(BAR_S_FREE + s));
       // and P of the previous tile must have been consumed before it is overwritten below
-      if (it > 0) FLB_WAIT(sm, BAR_PV_DONE + s, (it - 1) & 1);
+      if (git > 0) FLB_WAIT(sm, BAR_PV_DONE + s, (git - 1) & 1);
     }
     l *= sc;
     m = m_new;
@@ -865,6 +1057,10 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
   // m = -inf; its sum may hold the tiny terms of clamped polynomial exponentials, so the running
   // maximum decides: such a row gets sum 0, which the epilogue turns into a row of zeros.
   const bool no_key = m == -CUDART_INF_F;
+  if constexpr (C::ROWLOOP) {
+    // the epilogue must have taken the previous row's sums before they are replaced
+    if (row_index > 0) FLB_WAIT(sm, BAR_O_FREE + s, (row_index - 1) & 1);
+  }
   sscale[row] = no_key ? 0.f : l;
   mbar_arrive(sm.bar(BAR_SCALE_FULL + s));
   if constexpr (!C::DIFF) {
@@ -1054,6 +1250,62 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
   if (row == 0) tma_store_wait_read();
 }
 
+// Epilogue of the resident-bias kernel: one result tile per row and stage, staged in buffers of
+// its own so that the next row's Q tile can load while the store reads.
+template <class C>
+FLB_DEV void epilogue_role_rows(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* tmO,
+                                const KernelParams& p, int h, int r0, RowWalk rw) {
+  const int row = threadIdx.x & 127;
+  const uint32_t lane_base = static_cast<uint32_t>((threadIdx.x >> 5) & 3) * 32u;
+  const uint32_t tO[2] = {tmem + C::COL_O0 + (lane_base << 16), tmem + C::COL_O1 + (lane_base << 16)};
+  constexpr int ROWB = C::VBOX * 2;
+  const int sw = ROWB == 128 ? (row & 7) : ROWB == 64 ? ((row >> 1) & 3) : ((row >> 2) & 1);
+  const int pairs = rw.items(0);
+#pragma unroll 1
+  for (int item = 0; item < pairs; ++item) {
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      if (item >= rw.items(s)) continue;
+      FLB_WAIT(sm, BAR_SCALE_FULL + s, item & 1);
+      const float l = sm.scale(s)[row];
+      FLB_WAIT(sm, BAR_PV_DONE + s, ((item + 1) * rw.nt - 1) & 1);
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      // this stage's staging buffer is free once at most the other stage's store is still reading
+      if (row == 0) tma_store_wait_read_pending<1>();
+      named_bar_sync(3, 128);
+      uint8_t* tile = sm.ostage(s);
+#pragma unroll
+      for (int c0 = 0; c0 < C::EV; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld32_sync(tO[s] + c0, o);
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          uint4 w;
+          w.x = pack_bf16(u2f(o[c]) * inv, u2f(o[c + 1]) * inv);
+          w.y = pack_bf16(u2f(o[c + 2]) * inv, u2f(o[c + 3]) * inv);
+          w.z = pack_bf16(u2f(o[c + 4]) * inv, u2f(o[c + 5]) * inv);
+          w.w = pack_bf16(u2f(o[c + 6]) * inv, u2f(o[c + 7]) * inv);
+          const int col = c0 + c, box = col / C::VBOX, chunk = (col % C::VBOX) / 8;
+          *reinterpret_cast<uint4*>(tile + box * (128 * ROWB) + row * ROWB + ((chunk ^ sw) << 4)) = w;
+        }
+      }
+      // accumulator and row sums are in registers: the next row may overwrite them
+      tc_fence_before();
+      mbar_arrive(sm.bar(BAR_O_FREE + s));
+      fence_proxy_async_smem();
+      named_bar_sync(3, 128);
+      if (row == 0) {
+#pragma unroll
+        for (int vb = 0; vb < C::NVB; ++vb)
+          tma_store_4d(tmO, smem_u32(tile) + vb * (128 * ROWB), vb * C::VBOX, r0, h, rw.n0 + 2 * item + s);
+        tma_store_commit();
+      }
+    }
+  }
+  if (row == 0) tma_store_wait_read();
+}
+
 // ------------------------------------------------------------------------------------------
 // kernel
 // ------------------------------------------------------------------------------------------
@@ -1061,7 +1313,7 @@ template <class C>
 __global__ void __launch_bounds__(C::THREADS, C::STAGES == 2 ? 1 : 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                const __grid_constant__ KernelParams p) {
+                const __grid_constant__ CUtensorMap tmB, const __grid_constant__ KernelParams p) {
   extern __shared__ uint8_t smem_raw[];
   Smem<C> sm{reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                         ~static_cast<uintptr_t>(1023))};
@@ -1104,6 +1356,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       hi = max(hi, rg[s].hi);
     }
   if (hi == 0) lo = 0;
+  // Resident-bias kernel: blockIdx.x = ((batch element, head), query tile, chunk of rows), chunk
+  // fastest; the "tile ranges" of the two stages string together the tiles of their rows.
+  [[maybe_unused]] RowWalk rw{0, 0, 0};
+  [[maybe_unused]] int rb_b = 0, rb_h = 0;
+  if constexpr (C::ROWLOOP) {
+    const int chunk = static_cast<int>(blockIdx.x) % p.res_chunks;
+    const int rest = static_cast<int>(blockIdx.x) / p.res_chunks;
+    const int qtile = rest % p.nq_blocks;
+    const int bhh = rest / p.nq_blocks;
+    rb_b = bhh / p.H;
+    rb_h = bhh % p.H;
+    const int ra = chunk * p.res_rows;
+    rw.n0 = rb_b * p.evo_inner + ra;
+    rw.count = max(0, min(p.evo_inner, ra + p.res_rows) - ra);
+    rw.nt = (p.S + kTileN - 1) / kTileN;
+    r0[0] = r0[1] = qtile * kTileM;
+    rg[0] = TileRange{0, rw.items(0) * rw.nt};
+    rg[1] = TileRange{0, rw.items(1) * rw.nt};
+    lo = 0;
+    hi = rg[0].hi;
+  }
 
   // Set-up: the lanes of warp 0 initialise one mbarrier each while warp 1 allocates tensor memory
   // and the producer lane fetches the tensor maps.  The producer warp needs only the mbarriers: it
@@ -1118,7 +1391,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane < BAR_COUNT) {
       const bool all_threads = (lane >= BAR_P_FULL && lane < BAR_PV_DONE) ||
                                (lane >= BAR_P_HALF && lane < BAR_KV_FULL) || lane >= BAR_S_FREE;
-      mbar_init(sm.bar(lane), all_threads ? 128 : 1);  // 128 arriving threads, or one commit / TMA
+      // (resident-bias kernel: Q_EMPTY, which takes the place of P_HALF, is a single commit)
+      const bool single = C::ROWLOOP && lane >= BAR_Q_EMPTY && lane < BAR_Q_EMPTY + 2;
+      mbar_init(sm.bar(lane), all_threads && !single ? 128 : 1);  // 128 arriving threads, or one commit / TMA
     }
     if (C::DIFF && lane == 0) mbar_init(sm.xbar(), 128);
     fence_mbar_init();
@@ -1135,6 +1410,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       tma_prefetch_desc(&tmO);
+      if constexpr (C::ROWLOOP) tma_prefetch_desc(&tmB);
     }
     named_bar_sync(1, 64);
   } else {
@@ -1156,7 +1432,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp < C::W_SOFTMAX_END) {
     reg_inc<C::STAGES == 2 ? FLB_REGS_SOFTMAX : FLB_REGS_SOFTMAX1>();
     const int s = warp >> 2;
-    if (rg[s].hi > rg[s].lo) {
+    if constexpr (C::ROWLOOP) {
+      for (int ri = 0; ri < rw.items(s) && !sm.ctl()->abort; ++ri)
+        softmax_role<C>(sm, tmem, p, s, rw.n0 + 2 * ri + s, rb_h, r0[s], TileRange{0, rw.nt}, ri);
+    } else if (rg[s].hi > rg[s].lo) {
       if constexpr (C::B2B) pointwise_role<C>(sm, tmem, p, s, rg[s]);
       else softmax_role<C>(sm, tmem, p, s, n, h, r0[s], rg[s]);
     }
@@ -1164,12 +1443,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else if (C::STAGES == 2 && warp < 12) {
     reg_dec<FLB_REGS_EPILOGUE>();
-    epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
+    if constexpr (C::ROWLOOP) epilogue_role_rows<C>(sm, tmem, &tmO, p, rb_h, r0[0], rw);
+    else epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else {
     reg_dec<C::STAGES == 2 ? FLB_REGS_ISSUE : FLB_REGS_ISSUE1>();
     if (hi > lo) {
-      if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi);
-      if (warp == C::W_TMA && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, vcol0, r0, rg, lo, hi);
+      if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi, rw.nt);
+      if (warp == C::W_TMA && lane == 0) {
+        if constexpr (C::ROWLOOP) load_role_rows<C>(sm, &tmQ, &tmK, &tmV, &tmB, p, rb_b, rb_h, r0[0], rw);
+        else load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, vcol0, r0, rg, lo, hi);
+      }
     }
     __syncwarp();
   }

@@ -7,7 +7,8 @@ namespace flb {
 
 template <int E, int EV, int SCORE, int MASK, bool DIFF, int STAGES>
 cudaError_t launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
-                        const CUtensorMap& tmO, const KernelParams& p, int grid, int cluster,
+                        const CUtensorMap& tmO, const CUtensorMap& tmB, const KernelParams& p, int grid,
+                        int cluster,
                         cudaStream_t stream) {
   using C = AttnCfg<E, EV, SCORE, MASK, DIFF, STAGES>;
   auto kernel = attn_fwd_kernel<C>;
@@ -16,7 +17,7 @@ cudaError_t launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CU
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   if (cluster <= 1) {
-    kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
+    kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, tmB, p);
     return cudaGetLastError();
   }
   // neighbouring CTAs form a thread-block cluster (they exchange row sums through distributed
@@ -33,12 +34,12 @@ cudaError_t launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CU
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, tmO, p);
+  return cudaLaunchKernelEx(&cfg, kernel, tmQ, tmK, tmV, tmO, tmB, p);
 }
 
 #define FLB_INSTANTIATE(E, EV, SCORE, MASK, DIFF, STAGES)                                    \
   template cudaError_t launch_attn<E, EV, SCORE, MASK, DIFF, STAGES>(                         \
       const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, const CUtensorMap&,         \
-      const KernelParams&, int, int, cudaStream_t);
+      const CUtensorMap&, const KernelParams&, int, int, cudaStream_t);
 
 }  // namespace flb

@@ -14,7 +14,10 @@ enum ScoreMod : int {
   // kernel-internal modes (never in the public struct): the back-to-back product
   // O = f(Q K^T * scale) V without softmax, K given as [S][E] rows or as [E][S] (keys contiguous)
   SCORE_B2B = 4,
-  SCORE_B2BT = 5
+  SCORE_B2BT = 5,
+  // additive biases with the pair bias (shared by every row of a batch element) resident in shared
+  // memory: a CTA keeps one (head, query tile) and walks a range of rows
+  SCORE_BIAS_RES = 6
 };
 // pointwise function between the two products of the back-to-back mode
 enum Pointwise : int { PW_IDENTITY = 0, PW_RELU = 1, PW_TANH = 2, PW_SIGMOID = 3 };
@@ -54,6 +57,12 @@ struct KernelParams {
   const void* bias[2];
   int64_t bias_sb[2], bias_sr[2], bias_sh[2], bias_sl[2];
   int bias_vec[2];  // rows are 16-byte aligned: 128-bit loads allowed
+  // resident-bias kernel: bias[0] is the per-row key vector (or null; strides sb, sr, sh), the pair
+  // bias comes through a tensor map with coordinates (key, query, head * pair_h, batch * pair_b);
+  // every CTA walks res_rows rows of one batch element, res_chunks CTAs cover its evo_inner rows
+  int pair_h, pair_b;
+  int res_rows, res_chunks;
+  int res_slots;  // K/V slots of this launch's ring (the bias tiles lie behind them)
   // masks
   int causal;                // document mask: also require j <= i
   int window;                // sliding window (keys i-window .. i)

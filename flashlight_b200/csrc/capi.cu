@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
@@ -68,6 +69,7 @@ MapLayout map_layout(const flb200_attn_params* p) {
 // carry the true widths, so the loads fill the missing feature columns with zeros (they add nothing
 // to q.k, and the value columns beyond Ev are clipped by the output store).
 bool kernel_built(int D, int score, int mask) {
+  if (score == SCORE_BIAS_RES) return mask == MASK_NONE && (D == 32 || D == 64);
   if (score == SCORE_B2B || score == SCORE_B2BT) return mask == MASK_NONE && (D == 32 || D == 64 || D == 128);
   if (D == 32)
     return (score == SCORE_NONE && (mask == MASK_NONE || mask == MASK_CAUSAL)) ||
@@ -201,20 +203,82 @@ int validate(const flb200_attn_params* p) {
   return FLB200_OK;
 }
 
-// Query tiles per CTA (see AttnCfg::STAGES).  Two stages share every K/V tile and win on long,
-// regular work items (no mask, causal, prefix-LM, sliding window).  One stage per CTA, two CTAs
-// per SM, wins where items are short or ragged, because one CTA's set-up and epilogue overlap the
-// other's tiles: document masks, additive biases (Evoformer rows), and launches too small to give
-// every SM two-stage work.  FLB200_STAGES=1|2 overrides the choice for tuning.
+// Query tiles per CTA (see AttnCfg::STAGES).  Two stages share every K/V tile: half the traffic from
+// L2 to shared memory, which decides for heads of 128 on long rows of keys (no mask, causal, ALiBi,
+// prefix-LM beyond about a thousand keys).  One stage per CTA, two CTAs per SM, lets one CTA's
+// set-up, epilogue and waits hide behind the other's tiles; measured on the reference's grids it
+// wins for every head width up to 64 (8-20 %), and at width 128 for short rows of keys, sliding
+// windows, document masks, the softcap (whose tiles are long) and additive biases.
+// FLB200_STAGES=1|2 overrides the choice for tuning.
 int pick_stages(const flb200_attn_params* p) {
   if (p->diff || p->product_chain) return 2;
   if (const char* e = std::getenv("FLB200_STAGES")) {
     const int v = std::atoi(e);
     if (v == 1 || v == 2) return v;
   }
-  if (p->mask == FLB200_MASK_DOCUMENT || p->score_mod == FLB200_SCORE_BIAS) return 1;
+  if (p->E <= 64 && p->Ev <= 64) return 1;
+  if (p->mask == FLB200_MASK_DOCUMENT || p->mask == FLB200_MASK_SLIDING ||
+      p->score_mod == FLB200_SCORE_BIAS || p->score_mod == FLB200_SCORE_SOFTCAP)
+    return 1;
   const long long ctas2 = static_cast<long long>((p->L + 2 * kTileM - 1) / (2 * kTileM)) * p->N * p->Hq;
-  return ctas2 < 2 * 148 ? 1 : 2;
+  if (ctas2 < 2 * 148) return 1;  // too few two-stage CTAs to give every SM two waves
+  if (p->mask == FLB200_MASK_NONE && p->score_mod == FLB200_SCORE_NONE) return p->S <= 512 ? 1 : 2;
+  return p->S <= 1024 ? 1 : 2;
+}
+
+// Additive biases of the Evoformer kind: one "pair" bias that every row of a batch element shares
+// (row stride 0) and at most one key vector per row (query stride 0).  Such a problem runs on the
+// resident-bias kernel: a CTA keeps the pair-bias columns of its (head, query tile) in shared
+// memory and walks a range of rows.  FLB200_BIAS_RESIDENT=0 turns the choice off for tuning.
+struct ResidentPlan {
+  bool use = false;
+  int pair = -1, rowvec = -1;  // indices into p->bias
+  int rows = 0, chunks = 0;    // rows per CTA, CTAs per (batch element, head, query tile)
+  int slots = 0;               // K/V ring slots that fit beside the bias tiles
+};
+
+ResidentPlan plan_resident(const flb200_attn_params* p, int width) {
+  ResidentPlan r;
+  if (p->score_mod != FLB200_SCORE_BIAS || p->diff || p->product_chain || width > 64) return r;
+  if (const char* e = std::getenv("FLB200_BIAS_RESIDENT"))
+    if (std::atoi(e) == 0) return r;
+  const int R = p->bias_inner;
+  if (R < 4) return r;
+  for (int q = 0; q < 2; ++q) {
+    if (!p->bias[q]) continue;
+    const int64_t* st = p->bias_stride[q];  // {b, r, h, i}
+    if (st[3] != 0 && st[1] == 0) {
+      if (r.pair >= 0) return r;
+      r.pair = q;
+    } else if (st[3] == 0) {
+      if (r.rowvec >= 0) return r;
+      r.rowvec = q;
+    } else {
+      return r;  // a full bias per row: nothing to keep resident
+    }
+  }
+  if (r.pair < 0) return r;
+  const int64_t* st = p->bias_stride[r.pair];
+  if (!aligned16(p->bias[r.pair]) || !mult8(st[0]) || !mult8(st[2]) || !mult8(st[3]) || st[3] < p->S) return r;
+  // shared memory behind the Q tiles and the output staging: 32 KB per bias tile, the rest K/V slots
+  // (two rows' tiles each), of which there must be at least two
+  const int nt = (p->S + kTileN - 1) / kTileN;
+  if (nt > 4) return r;
+  const int tile_bytes = kTileM * width * 2;
+  const int room = 232448 - 1024 - 2 * tile_bytes - 2 * tile_bytes - 2048 - nt * 32768;
+  r.slots = std::min(7, room / (2 * tile_bytes));
+  if (room < 0 || r.slots < 2) return r;
+  const int H = p->Hq, B = p->N / R;
+  const long long base = static_cast<long long>((p->L + kTileM - 1) / kTileM) * B * H;
+  int chunks;
+  if (base >= 148) chunks = static_cast<int>(std::max(1LL, std::min<long long>(R / 8, (4 * 148) / base)));
+  else chunks = static_cast<int>(std::max(1LL, std::min<long long>(R / 2, 148 / base)));
+  int rows = (R + chunks - 1) / chunks;
+  rows += rows & 1;  // the two stages take the rows in pairs
+  r.rows = rows;
+  r.chunks = (R + rows - 1) / rows;
+  r.use = true;
+  return r;
 }
 
 int check_arch() {
@@ -250,7 +314,7 @@ cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUten
                           int grid, int cluster, cudaStream_t st) {
 #define FLB_CASE(SC, MK)          \
   if (score == SC && mask == MK)  \
-    return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, kp, grid, cluster, st);
+    return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, a, kp, grid, cluster, st);
   if constexpr (DIFF) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
@@ -407,8 +471,10 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
   }
 
   // tensor maps: innermost feature axis, then row, head, batch
-  const int kscore = kernel_score(p);
+  int kscore = kernel_score(p);
   const int width = kernel_width(p->E, p->Ev, kscore, p->mask, p->diff);  // q/k width
+  const ResidentPlan res = plan_resident(p, width);
+  if (res.use) kscore = SCORE_BIAS_RES;
   // value columns one CTA handles: twice the q/k width for the differential kernels, except the
   // widest, whose CTAs come in pairs that split value heads above 128
   const int vwidth = p->diff ? (width == 128 ? 128 : 2 * width) : width;
@@ -418,7 +484,32 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
   const uint32_t kbox = width >= 64 ? 64 : width;
   const uint32_t vbox = vwidth >= 64 ? 64 : vwidth;
   const int Hv = p->diff ? H : p->Hkv;
-  CUtensorMap tmQ, tmK, tmV, tmO;
+  CUtensorMap tmQ, tmK, tmV, tmO, tmB;
+  if (res.use) {
+    const int R = p->bias_inner, B = p->N / R;
+    const int64_t* st = p->bias_stride[res.pair];
+    kp.pair_h = st[2] != 0;
+    kp.pair_b = st[0] != 0;
+    kp.res_rows = res.rows;
+    kp.res_chunks = res.chunks;
+    kp.res_slots = res.slots;
+    kp.nq_blocks = (p->L + kTileM - 1) / kTileM;
+    // the key vector moves to slot 0 (strides b, r, h); slot 1 is unused by this kernel
+    const int rv = res.rowvec;
+    kp.bias[0] = rv >= 0 ? p->bias[rv] : nullptr;
+    kp.bias_sb[0] = rv >= 0 ? p->bias_stride[rv][0] : 0;
+    kp.bias_sr[0] = rv >= 0 ? p->bias_stride[rv][1] : 0;
+    kp.bias_sh[0] = rv >= 0 ? p->bias_stride[rv][2] : 0;
+    kp.bias_vec[0] = rv >= 0 && aligned16(p->bias[rv]) && mult8(p->bias_stride[rv][0]) &&
+                     mult8(p->bias_stride[rv][1]) && mult8(p->bias_stride[rv][2]);
+    kp.bias[1] = nullptr;
+    // pair bias as (key, query, head, batch element); broadcast axes get extent 1
+    const uint64_t dh = kp.pair_h ? p->Hq : 1, db = kp.pair_b ? B : 1;
+    const uint64_t sh = kp.pair_h ? st[2] : ((static_cast<uint64_t>(st[3]) * p->L + 7) & ~7ull);
+    const uint64_t sb = kp.pair_b ? st[0] : sh * dh;
+    if (make_tmap_bf16_4d(&tmB, p->bias[res.pair], p->S, p->L, dh, db, st[3], sh, sb, 64, kTileM))
+      return FLB200_E_LAUNCH;
+  }
   if (make_tmap_bf16_4d(&tmQ, p->q, p->E, p->L, p->Hq, p->N, p->q_stride[2], p->q_stride[1],
                         p->q_stride[0], kbox, kTileM) ||
       (p->k_keys_contiguous
@@ -432,6 +523,7 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
       make_tmap_bf16_4d(&tmO, p->o, p->Ev, p->L, H, p->N, p->o_stride[2], p->o_stride[1],
                         p->o_stride[0], vbox, kTileM))
     return FLB200_E_LAUNCH;
+  if (!res.use) tmB = tmQ;  // unused by every other kernel
 
   {
     // Sections pay when the K/V of all (batch, head) pairs exceed L2 and every query block reads
@@ -455,7 +547,8 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
       if (sec < bh_count) kp.sec_bh = static_cast<int>(sec);
     }
   }
-  const int grid = kp.nq_blocks * p->N * H * kp.v_halves;
+  const int grid = res.use ? kp.nq_blocks * (p->N / p->bias_inner) * H * res.chunks
+                           : kp.nq_blocks * p->N * H * kp.v_halves;
   const int cluster = kp.v_exchange ? 2 : 1;
   cudaError_t e = cudaErrorInvalidValue;
   const int sc = kscore, mk = p->mask;
@@ -463,6 +556,9 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
     if (width == 128) e = dispatch_mods<128, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else if (width == 64) e = dispatch_mods<64, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else e = dispatch_mods<32, 64, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+  } else if (res.use) {
+    if (width == 64) e = launch_attn<64, 64, SCORE_BIAS_RES, MASK_NONE, false, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
+    else e = launch_attn<32, 32, SCORE_BIAS_RES, MASK_NONE, false, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
   } else if (stages == 2) {
     if (width == 128) e = dispatch_mods<128, 128, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else if (width == 64) e = dispatch_mods<64, 64, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);

@@ -192,6 +192,11 @@ FLB_DEV void tma_store_4d(const void* tmap, uint32_t src, int c0, int c1, int c2
 FLB_DEV void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until the bulk stores committed so far have read their shared-memory source.
 FLB_DEV void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... until at most N of them are still reading
+template <int N>
+FLB_DEV void tma_store_wait_read_pending() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 
 // ----------------------------------------------------------------------------
 // TMEM allocation (one warp executes these, .sync.aligned)

@@ -86,8 +86,7 @@ def test_tiny_diff_sweep(tmp_path):
                           "--output", str(tmp_path / "d")])
     rows = RD.main(args)
     assert [r[6] for r in rows] == [64, 128]
-    assert rows[0][1] > 0                       # head dim 64 runs
-    assert rows[1][1] != rows[1][1]             # head dim 128: no kernel, reported as nan
+    assert rows[0][1] > 0 and rows[1][1] > 0    # head dims 64 and 128 (value heads of 128 and 256) both run
     assert rows[0][-1] in ("B200", "unknown")
 
 
