@@ -71,7 +71,7 @@ struct AttnCfg {
   // the two stages work on two rows at a time, each with its own Q, K and V.
   static constexpr bool ROWLOOP = SCORE_ == SCORE_BIAS_RES;
   static constexpr bool BIAS = SCORE_ == SCORE_BIAS || ROWLOOP;
-  static_assert(!ROWLOOP || (STAGES_ == 2 && !DIFF_ && EV_ <= 64 && E_ <= 64), "resident bias: narrow heads, two stages");
+  static_assert(!ROWLOOP || (STAGES_ == 2 && !DIFF_ && EV_ <= 64 && E_ == EV_), "resident bias: narrow heads, two stages");
   static constexpr bool B2B = SCORE_ == SCORE_B2B || SCORE_ == SCORE_B2BT;
   static constexpr bool KT = SCORE_ == SCORE_B2BT;
   static constexpr int KBOX = E >= 64 ? 64 : E;     // elements per swizzled row of a Q/K box
@@ -81,10 +81,9 @@ struct AttnCfg {
   static constexpr int V_BOX_BYTES = 128 * VBOX * 2;
   static constexpr int Q_BYTES = 128 * E * 2;                    // one stage
   static constexpr int K_HEAD_BYTES = 128 * E * 2;               // one head's K tile
-  // diff: two heads' K side by side; resident bias: the two stages' (rows') K and V side by side
-  static constexpr int K_BYTES = K_HEAD_BYTES * ((DIFF || ROWLOOP) ? 2 : 1);
+  static constexpr int K_BYTES = K_HEAD_BYTES * (DIFF ? 2 : 1);  // diff: two heads side by side
   static constexpr int V_HEAD_BYTES = 128 * EV * 2;
-  static constexpr int V_BYTES = V_HEAD_BYTES * (ROWLOOP ? 2 : 1);
+  static constexpr int V_BYTES = V_HEAD_BYTES;
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
   static constexpr int SMEM_BUDGET = STAGES == 2 ? 224 * 1024 : 110 * 1024;
   static constexpr int NSTAGE_FIT = (SMEM_BUDGET - STAGES * Q_BYTES) / SLOT_BYTES;
@@ -141,11 +140,14 @@ enum : int {
   BAR_KV_FULL = 14,    // +slot
   BAR_KV_EMPTY = 22,   // +slot
   BAR_S_FREE = 30,     // +s   softmax -> MMA: S tile read into registers (only with SEP_P)
-  BAR_COUNT = 32,
-  // resident-bias kernel (uses neither P_HALF nor O_STAGED, and at most four K/V slots)
+  BAR_COUNT = 48,
+  // resident-bias kernel: it uses neither P_HALF nor O_STAGED, and each stage has a K/V ring, a
+  // producer and an MMA warp of its own (up to seven slots per stage)
   BAR_Q_EMPTY = BAR_P_HALF,    // +s   MMA -> producer: the row's last QK product has read Q
   BAR_O_FREE = BAR_O_STAGED,   // +s   epilogue -> MMA / softmax: the row's accumulator and row sums are read
-  BAR_BIAS_FULL = 21           //      producer -> softmax: the pair-bias tiles are in shared memory
+  BAR_RING_FULL = 14,          // +8s+slot  (14..20 and 22..28)
+  BAR_BIAS_FULL = 21,          //      producer -> softmax: the pair-bias tiles are in shared memory
+  BAR_RING_EMPTY = 32          // +8s+slot  (32..38 and 40..46)
 };
 
 struct TileRange {
@@ -210,16 +212,20 @@ struct Smem {
   FLB_DEV uint8_t* slot(int i) const {
     return base + C::STAGES * C::Q_BYTES + C::OSTAGE_BYTES + i * C::SLOT_BYTES;
   }
-  // resident bias tiles: behind the `slots` K/V slots this launch uses
-  FLB_DEV uint8_t* bias(int slots) const { return slot(slots); }
+  // resident-bias kernel: slot i of stage s's ring (`slots` slots of one tile each per stage), and
+  // the bias tiles behind the two rings
+  FLB_DEV uint8_t* ring(int s, int i, int slots) const {
+    return base + C::STAGES * C::Q_BYTES + C::OSTAGE_BYTES + (s * slots + i) * C::K_HEAD_BYTES;
+  }
+  FLB_DEV uint8_t* bias(int slots) const { return ring(2, 0, slots); }
   FLB_DEV uint8_t* aux() const { return base + (C::SMEM_USED - 1024 - C::AUX_BYTES); }
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
-  FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }
-  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
+  FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 384); }
+  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 388); }
   FLB_DEV float* scale(int s) const { return reinterpret_cast<float*>(aux() + 512) + s * 128; }
   // pair exchange (differential attention with value heads of two kernel widths): a barrier the
   // partner CTA arrives at and the 128 row sums it stores here
-  FLB_DEV uint32_t xbar() const { return smem_u32(aux()) + 280; }
+  FLB_DEV uint32_t xbar() const { return smem_u32(aux()) + 408; }
   FLB_DEV float* xchg() const { return reinterpret_cast<float*>(aux() + 1536); }
 };
 
@@ -311,61 +317,50 @@ struct RowWalk {
   FLB_DEV int items(int s) const { return (count + 1 - s) >> 1; }
 };
 
-// Producer of the resident-bias kernel: the pair-bias tiles of this (head, query tile) once, then
-// per pair of rows their Q tiles and, tile by tile, both rows' K and V side by side in one slot.
+// Producer of one stage of the resident-bias kernel: per row its Q tile and, tile by tile, K and V
+// into the stage's ring.  The producer of stage 0 first brings in the pair-bias tiles.
 template <class C>
 FLB_DEV void load_role_rows(const Smem<C>& sm, const CUtensorMap* tmQ, const CUtensorMap* tmK,
                             const CUtensorMap* tmV, const CUtensorMap* tmB, const KernelParams& p,
-                            int b, int h, int r0, RowWalk rw) {
+                            int s, int b, int h, int r0, RowWalk rw) {
   if (p.withhold_loads) return;
-  mbar_arrive_expect_tx(sm.bar(BAR_BIAS_FULL), rw.nt * 32768);
+  if (s == 0) {
+    mbar_arrive_expect_tx(sm.bar(BAR_BIAS_FULL), rw.nt * 32768);
 #pragma unroll 1
-  for (int t = 0; t < rw.nt; ++t)
+    for (int t = 0; t < rw.nt; ++t)
 #pragma unroll
-    for (int kb = 0; kb < 2; ++kb)
-      tma_load_4d(smem_u32(sm.bias(p.res_slots)) + (t * 2 + kb) * 16384, tmB, sm.bar(BAR_BIAS_FULL),
-                  t * kTileN + kb * 64, r0, h * p.pair_h, b * p.pair_b);
+      for (int kb = 0; kb < 2; ++kb)
+        tma_load_4d(smem_u32(sm.bias(p.res_slots)) + (t * 2 + kb) * 16384, tmB, sm.bar(BAR_BIAS_FULL),
+                    t * kTileN + kb * 64, r0, h * p.pair_h, b * p.pair_b);
+  }
   int slot = 0;
   uint32_t ph = 0;  // ring position of the next load and how often the ring has wrapped (parity)
-  const int pairs = rw.items(0);
+  const int rows = rw.items(s);
 #pragma unroll 1
-  for (int item = 0; item < pairs; ++item) {
-    const int live = item < rw.items(1) ? 2 : 1;  // the last pair of an odd count has one row
+  for (int r = 0; r < rows; ++r) {
+    const int n = rw.n0 + 2 * r + s;
+    // the Q tile is free once the previous row's last QK product has read it
+    if (r > 0) FLB_WAIT(sm, BAR_Q_EMPTY + s, (r - 1) & 1);
+    mbar_arrive_expect_tx(sm.bar(BAR_Q_FULL + s), C::Q_BYTES);
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      if (s < live) {
-        // the Q tile is free once the previous row's last QK product has read it
-        if (item > 0) FLB_WAIT(sm, BAR_Q_EMPTY + s, (item - 1) & 1);
-        mbar_arrive_expect_tx(sm.bar(BAR_Q_FULL + s), C::Q_BYTES);
-#pragma unroll
-        for (int kb = 0; kb < C::NKB; ++kb)
-          tma_load_4d(smem_u32(sm.q(s)) + kb * C::QK_BOX_BYTES, tmQ, sm.bar(BAR_Q_FULL + s),
-                      kb * C::KBOX, r0, h, rw.n0 + 2 * item + s);
-      }
-    }
+    for (int kb = 0; kb < C::NKB; ++kb)
+      tma_load_4d(smem_u32(sm.q(s)) + kb * C::QK_BOX_BYTES, tmQ, sm.bar(BAR_Q_FULL + s), kb * C::KBOX, r0, h, n);
 #pragma unroll 1
     for (int t = 0; t < rw.nt; ++t) {
 #pragma unroll
-      for (int kv = 0; kv < 2; ++kv) {  // K(t) of both rows, then V(t) of both rows
-        FLB_WAIT(sm, BAR_KV_EMPTY + slot, ph ^ 1);
-        mbar_arrive_expect_tx(sm.bar(BAR_KV_FULL + slot), live * (kv ? C::V_HEAD_BYTES : C::K_HEAD_BYTES));
-        const uint32_t dst = smem_u32(sm.slot(slot));
+      for (int kv = 0; kv < 2; ++kv) {  // K(t), then V(t)
+        FLB_WAIT(sm, BAR_RING_EMPTY + 8 * s + slot, ph ^ 1);
+        const uint32_t full = sm.bar(BAR_RING_FULL + 8 * s + slot);
+        mbar_arrive_expect_tx(full, C::K_HEAD_BYTES);
+        const uint32_t dst = smem_u32(sm.ring(s, slot, p.res_slots));
+        if (kv == 0) {
 #pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          if (s < live) {
-            const int n = rw.n0 + 2 * item + s;
-            if (kv == 0) {
+          for (int kb = 0; kb < C::NKB; ++kb)
+            tma_load_4d(dst + kb * C::QK_BOX_BYTES, tmK, full, kb * C::KBOX, t * kTileN, h, n);
+        } else {
 #pragma unroll
-              for (int kb = 0; kb < C::NKB; ++kb)
-                tma_load_4d(dst + s * C::K_HEAD_BYTES + kb * C::QK_BOX_BYTES, tmK,
-                            sm.bar(BAR_KV_FULL + slot), kb * C::KBOX, t * kTileN, h, n);
-            } else {
-#pragma unroll
-              for (int vb = 0; vb < C::NVB; ++vb)
-                tma_load_4d(dst + s * C::V_HEAD_BYTES + vb * C::V_BOX_BYTES, tmV,
-                            sm.bar(BAR_KV_FULL + slot), vb * C::VBOX, t * kTileN, h, n);
-            }
-          }
+          for (int vb = 0; vb < C::NVB; ++vb)
+            tma_load_4d(dst + vb * C::V_BOX_BYTES, tmV, full, vb * C::VBOX, t * kTileN, h, n);
         }
         if (++slot == p.res_slots) {
           slot = 0;
@@ -373,6 +368,88 @@ FLB_DEV void load_role_rows(const Smem<C>& sm, const CUtensorMap* tmQ, const CUt
         }
       }
     }
+  }
+}
+
+// MMA issue for one stage of the resident-bias kernel (each stage has an issuing warp of its own, so
+// neither waits for the other's softmax).  The stage's rows are strung together tile after tile; per
+// position u: S = Q K(u)^T as soon as the softmax warps have read the previous scores, then
+// O += P(u-1) V(u-1).  P has tensor-memory columns of its own (narrow heads).
+template <class C>
+FLB_DEV void mma_role_rows(const Smem<C>& sm, uint32_t tmem, const KernelParams& p, int s, RowWalk rw) {
+  const uint32_t leader = elect_one() ? 1u : 0u;
+  constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, 0);
+  constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
+  const uint32_t tS = tmem + (s ? C::COL_S1 : C::COL_S0), tO = tmem + (s ? C::COL_O1 : C::COL_O0);
+  const uint32_t tP = tmem + (s ? C::COL_P1 : C::COL_P0);
+  constexpr uint64_t kdesc0 = (static_cast<uint64_t>((8 * C::KBOX * 2) >> 4) << 32) |
+                              (1ull << 16) | (1ull << 46) | (static_cast<uint64_t>(C::SWZ_K) << 61);
+  constexpr uint64_t vdesc0 = (static_cast<uint64_t>((8 * C::VBOX * 2) >> 4) << 32) |
+                              (static_cast<uint64_t>(C::V_BOX_BYTES >> 4) << 16) | (1ull << 46) |
+                              (static_cast<uint64_t>(C::SWZ_V) << 61);
+  constexpr uint32_t k_hi = static_cast<uint32_t>(kdesc0 >> 32), k_lo0 = static_cast<uint32_t>(kdesc0);
+  constexpr uint32_t v_hi = static_cast<uint32_t>(vdesc0 >> 32), v_lo0 = static_cast<uint32_t>(vdesc0);
+  const uint32_t q_lo = k_lo0 + ((smem_u32(sm.q(s)) & 0x3FFFFu) >> 4);
+  const uint32_t ring0 = (smem_u32(sm.ring(s, 0, p.res_slots)) & 0x3FFFFu) >> 4;
+  const int total = rw.items(s) * rw.nt;
+  // ring slots in load order K(0) V(0) K(1) V(1) ...: K(u) is load 2u, V(u-1) load 2u - 1
+  int kslot = 0, vslot = p.res_slots > 1 ? p.res_slots - 1 : 0;  // load -1 precedes load 0
+  uint32_t kph = 0, vph = 1;
+  auto advance2 = [&](int& slot, uint32_t& ph) {
+    slot += 2;
+    if (slot >= p.res_slots) {
+      slot -= p.res_slots;
+      ph ^= 1;
+    }
+  };
+  int qk_t = 0, qk_row = 0, pv_t = 0, pv_row = 0;
+#pragma unroll 1
+  for (int u = 0; u <= total; ++u) {
+    if (u < total) {
+      // S = Q K(u)^T
+      FLB_WAIT(sm, BAR_RING_FULL + 8 * s + kslot, kph);
+      if (qk_t == 0) FLB_WAIT(sm, BAR_Q_FULL + s, qk_row & 1);  // first tile of a row: its Q tile
+      if (u > 0) FLB_WAIT(sm, BAR_S_FREE + s, (u - 1) & 1);     // the previous scores are in registers
+      tc_fence_after();
+      const uint32_t k_lo = k_lo0 + ring0 + kslot * (C::K_HEAD_BYTES >> 4);
+      umma_ss_c<0>(leader, tS, q_lo, k_lo, k_hi, idesc_qk);
+#pragma unroll
+      for (int k = 1; k < C::E / 16; ++k) {
+        const int kk = k * 16;
+        const uint32_t off = ((kk / C::KBOX) * C::QK_BOX_BYTES + (kk % C::KBOX) * 2) >> 4;
+        umma_ss_c<1>(leader, tS, q_lo + off, k_lo + off, k_hi, idesc_qk);
+      }
+      umma_commit_c(leader, sm.bar(BAR_S_FULL + s));
+      umma_commit_c(leader, sm.bar(BAR_RING_EMPTY + 8 * s + kslot));
+      if (++qk_t == rw.nt) {  // last tile of the row: its Q tile may be replaced
+        qk_t = 0;
+        ++qk_row;
+        umma_commit_c(leader, sm.bar(BAR_Q_EMPTY + s));
+      }
+    }
+    if (u > 0) {
+      // O += P(u-1) V(u-1); the first product of a row overwrites the accumulator, which the
+      // epilogue must have read for the previous row
+      FLB_WAIT(sm, BAR_RING_FULL + 8 * s + vslot, vph);
+      FLB_WAIT(sm, BAR_P_FULL + s, (u - 1) & 1);
+      const bool fresh = pv_t == 0;
+      if (fresh && pv_row > 0) FLB_WAIT(sm, BAR_O_FREE + s, (pv_row - 1) & 1);
+      tc_fence_after();
+      const uint32_t v_lo = v_lo0 + ring0 + vslot * (C::K_HEAD_BYTES >> 4);
+      if (!fresh) umma_ts_c<1>(leader, tO, tP, v_lo, v_hi, idesc_pv);
+      else umma_ts_c<0>(leader, tO, tP, v_lo, v_hi, idesc_pv);
+#pragma unroll
+      for (int k = 1; k < kTileN / 16; ++k)
+        umma_ts_c<1>(leader, tO, tP + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
+      umma_commit_c(leader, sm.bar(BAR_PV_DONE + s));
+      umma_commit_c(leader, sm.bar(BAR_RING_EMPTY + 8 * s + vslot));
+      if (++pv_t == rw.nt) {
+        pv_t = 0;
+        ++pv_row;
+      }
+    }
+    advance2(kslot, kph);
+    advance2(vslot, vph);
   }
 }
 
@@ -385,7 +462,7 @@ FLB_DEV void load_role_rows(const Smem<C>& sm, const CUtensorMap* tmQ, const CUt
 // ------------------------------------------------------------------------------------------
 template <class C>
 FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
-                      const TileRange (&rg)[2], int lo, int hi, [[maybe_unused]] int row_tiles = 0) {
+                      const TileRange (&rg)[2], int lo, int hi) {
   const uint32_t leader = elect_one() ? 1u : 0u;  // the lane that issues; all lanes run the loop
   constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, C::KT ? 1 : 0);
   constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
@@ -413,11 +490,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                             k_lo0 + ((smem_u32(sm.q(1)) & 0x3FFFFu) >> 4)};
   const uint32_t slot0 = (smem_u32(sm.slot(0)) & 0x3FFFFu) >> 4;
   bool q_ready[2] = {false, false};
-  // resident-bias kernel: the walk strings the rows' tiles together (`row_tiles` per row); tile
-  // index inside the row and row index of the next PV and QK product of each stage
-  [[maybe_unused]] int pv_t[2] = {0, 0}, pv_row[2] = {0, 0}, qk_t[2] = {0, 0}, qk_row[2] = {0, 0};
-  [[maybe_unused]] int ring_slot = 0;
-  [[maybe_unused]] uint32_t ring_ph = 0;
 
   // position u of the walk holds tile lo + u (or hi - 1 - u when the walk is reversed); stage s
   // takes part in positions [first[s], first[s] + cnt[s])
@@ -428,29 +500,9 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
 #pragma unroll 1
   for (int u = 0; u <= n_pos; ++u) {
     const bool have_k = u < n_pos, have_v = u > 0;
-    int kslot, vslot;
-    uint32_t kph, vph;
-    if constexpr (C::ROWLOOP) {
-      // ring of p.res_slots slots, taken in load order: V(u - 1), then K(u)
-      vslot = ring_slot;
-      vph = ring_ph;
-      if (have_v && ++ring_slot == p.res_slots) {
-        ring_slot = 0;
-        ring_ph ^= 1;
-      }
-      kslot = ring_slot;
-      kph = ring_ph;
-      if (have_k && ++ring_slot == p.res_slots) {
-        ring_slot = 0;
-        ring_ph ^= 1;
-      }
-    } else {
-      const int kseq = 2 * u, vseq = 2 * (u - 1) + 1;
-      kslot = kseq % C::NSTAGE;
-      vslot = have_v ? vseq % C::NSTAGE : 0;
-      kph = (kseq / C::NSTAGE) & 1;
-      vph = (vseq / C::NSTAGE) & 1;
-    }
+    const int kseq = 2 * u, vseq = 2 * (u - 1) + 1;
+    const int kslot = kseq % C::NSTAGE, vslot = have_v ? vseq % C::NSTAGE : 0;
+    const uint32_t kph = (kseq / C::NSTAGE) & 1, vph = (vseq / C::NSTAGE) & 1;
     const uint32_t v_lo = v_lo0 + slot0 + vslot * (C::SLOT_BYTES >> 4);
     const uint32_t k_lo = k_lo0 + slot0 + kslot * (C::SLOT_BYTES >> 4);
     if (have_v) FLB_WAIT(sm, BAR_KV_FULL + vslot, vph);
@@ -465,18 +517,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
           // O_s += P_s(t-1) V(t-1)
           if (have_v && u - 1 >= first[s] && u - 1 < first[s] + cnt[s]) {
             const int it = u - 1 - first[s];
-            bool fresh = it == 0;  // first product of a row: the accumulator is overwritten
-            if constexpr (C::ROWLOOP) {
-              fresh = pv_t[s] == 0;
-              // ... which the epilogue must have read for the previous row
-              if (fresh && pv_row[s] > 0) FLB_WAIT(sm, BAR_O_FREE + s, (pv_row[s] - 1) & 1);
-              if (++pv_t[s] == row_tiles) {
-                pv_t[s] = 0;
-                ++pv_row[s];
-              }
-            }
             const uint32_t tA = C::SEP_P ? tP[s] : tS[s];  // where the softmax warps put P
-            const uint32_t vs_lo = v_lo + (C::ROWLOOP ? s * (C::V_HEAD_BYTES >> 4) : 0);
             // the product starts on the first 64 keys while the softmax warps finish the rest
             if constexpr (C::EARLY_PV) {
               FLB_WAIT(sm, BAR_P_HALF + s, it & 1);
@@ -484,15 +525,15 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
               FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
             }
             tc_fence_after();
-            if (!fresh) umma_ts_c<1>(leader, tO[s], tA, vs_lo, v_hi, idesc_pv);
-            else umma_ts_c<0>(leader, tO[s], tA, vs_lo, v_hi, idesc_pv);
+            if (it > 0) umma_ts_c<1>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
+            else umma_ts_c<0>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
 #pragma unroll
             for (int k = 1; k < kTileN / 32; ++k)
-              umma_ts_c<1>(leader, tO[s], tA + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
+              umma_ts_c<1>(leader, tO[s], tA + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
             if constexpr (C::SPLIT_P) {
 #pragma unroll
               for (int k = 0; k < kTileN / 32; ++k)
-                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
+                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
                              idesc_pv);
             }
             if constexpr (C::EARLY_PV) {
@@ -501,11 +542,11 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
             }
 #pragma unroll
             for (int k = kTileN / 32; k < kTileN / 16; ++k)
-              umma_ts_c<1>(leader, tO[s], tA + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
+              umma_ts_c<1>(leader, tO[s], tA + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi, idesc_pv);
             if constexpr (C::SPLIT_P) {
 #pragma unroll
               for (int k = kTileN / 32; k < kTileN / 16; ++k)
-                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, vs_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
+                umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
                              idesc_pv);
             }
             umma_commit_c(leader, sm.bar(BAR_PV_DONE + s));
@@ -513,12 +554,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
         } else {
           // S_s = Q_s K(t)^T
           if (have_k && u >= first[s] && u < first[s] + cnt[s]) {
-            if constexpr (C::ROWLOOP) {
-              if (qk_t[s] == 0) {  // first tile of a row: its Q tile must have landed
-                FLB_WAIT(sm, BAR_Q_FULL + s, qk_row[s] & 1);
-                tc_fence_after();
-              }
-            } else if (!q_ready[s]) {
+            if (!q_ready[s]) {
               FLB_WAIT(sm, BAR_Q_FULL + s, 0);
               q_ready[s] = true;
               tc_fence_after();
@@ -541,7 +577,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                 umma_ss2_c<1>(leader, tS[s], q_lo[s] + off, k_hi, kt_lo + ((kk * 128) >> 4), kt_hi, idesc_qk);
               }
             } else {
-              const uint32_t ks_lo = k_lo + ((C::DIFF || C::ROWLOOP) ? s * (C::K_HEAD_BYTES >> 4) : 0);
+              const uint32_t ks_lo = k_lo + (C::DIFF ? s * (C::K_HEAD_BYTES >> 4) : 0);
               umma_ss_c<0>(leader, tS[s], q_lo[s], ks_lo, k_hi, idesc_qk);
 #pragma unroll
               for (int k = 1; k < C::E / 16; ++k) {
@@ -551,13 +587,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
               }
             }
             umma_commit_c(leader, sm.bar(BAR_S_FULL + s));
-            if constexpr (C::ROWLOOP) {
-              if (++qk_t[s] == row_tiles) {  // last tile of the row: its Q tile may be replaced
-                qk_t[s] = 0;
-                ++qk_row[s];
-                umma_commit_c(leader, sm.bar(BAR_Q_EMPTY + s));
-              }
-            }
           }
         }
       }
@@ -1378,6 +1407,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     hi = rg[0].hi;
   }
 
+  // the warps that issue loads (the resident-bias kernel has one per stage, and one MMA warp per stage:
+  // warps 12 / 13 serve stage 0, warps 14 / 15 stage 1)
+  const bool is_producer = warp == C::W_TMA || (C::ROWLOOP && warp == C::W_TMA + 2);
+  constexpr int kEarly = C::ROWLOOP ? 96 : 64;  // warp 0 and the producer warps meet on barrier 1
   // Set-up: the lanes of warp 0 initialise one mbarrier each while warp 1 allocates tensor memory
   // and the producer lane fetches the tensor maps.  The producer warp needs only the mbarriers: it
   // meets warp 0 on a barrier of their own and starts the first loads while the rest of the CTA
@@ -1388,23 +1421,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       sm.ctl()->fail_bar = -1;
       sm.ctl()->limit_us = p.wait_limit_us;
     }
-    if (lane < BAR_COUNT) {
+    if (lane < 32) {
       const bool all_threads = (lane >= BAR_P_FULL && lane < BAR_PV_DONE) ||
                                (lane >= BAR_P_HALF && lane < BAR_KV_FULL) || lane >= BAR_S_FREE;
       // (resident-bias kernel: Q_EMPTY, which takes the place of P_HALF, is a single commit)
       const bool single = C::ROWLOOP && lane >= BAR_Q_EMPTY && lane < BAR_Q_EMPTY + 2;
       mbar_init(sm.bar(lane), all_threads && !single ? 128 : 1);  // 128 arriving threads, or one commit / TMA
+      if (C::ROWLOOP && lane < 16) mbar_init(sm.bar(32 + lane), 1);  // ring slots handed back by commits
     }
     if (C::DIFF && lane == 0) mbar_init(sm.xbar(), 128);
     fence_mbar_init();
-    named_bar_sync(1, 64);
+    named_bar_sync(1, kEarly);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(sm.tmem_base()), C::TMEM_COLS);
     tmem_relinquish();
   }
   uint32_t tmem = 0;
-  if (warp == C::W_TMA) {
+  if (is_producer) {
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
@@ -1412,10 +1446,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tma_prefetch_desc(&tmO);
       if constexpr (C::ROWLOOP) tma_prefetch_desc(&tmB);
     }
-    named_bar_sync(1, 64);
+    named_bar_sync(1, kEarly);
   } else {
     tc_fence_before();
-    named_bar_sync(2, C::THREADS - 32);
+    named_bar_sync(2, C::THREADS - (kEarly - 32));
     tc_fence_after();
     tmem = *sm.tmem_base();
   }
@@ -1425,7 +1459,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   // A launch in which some CTA already gave up is not worth finishing: one thread of the MMA warp's
   // group that has nothing else to do looks at the status word and raises the abort flag, which
   // ends every role at its next long wait.  The look-up stays off the path to the first MMA.
-  if (threadIdx.x == (C::W_MMA + 2) * 32 && p.status != nullptr &&
+  if (threadIdx.x == (C::W_MMA + 3) * 32 + 1 && p.status != nullptr &&
       *reinterpret_cast<volatile int*>(p.status) != 0)
     sm.ctl()->abort = 1;
 
@@ -1447,12 +1481,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     else epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else {
     reg_dec<C::STAGES == 2 ? FLB_REGS_ISSUE : FLB_REGS_ISSUE1>();
-    if (hi > lo) {
-      if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi, rw.nt);
-      if (warp == C::W_TMA && lane == 0) {
-        if constexpr (C::ROWLOOP) load_role_rows<C>(sm, &tmQ, &tmK, &tmV, &tmB, p, rb_b, rb_h, r0[0], rw);
-        else load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, vcol0, r0, rg, lo, hi);
+    if constexpr (C::ROWLOOP) {
+      const int s = (warp - C::W_MMA) >> 1;  // warps 12, 13: stage 0; 14, 15: stage 1
+      if (rw.items(s) > 0) {
+        if (((warp - C::W_MMA) & 1) == 0) mma_role_rows<C>(sm, tmem, p, s, rw);
+        else if (lane == 0) load_role_rows<C>(sm, &tmQ, &tmK, &tmV, &tmB, p, s, rb_b, rb_h, r0[0], rw);
       }
+    } else if (hi > lo) {
+      if (warp == C::W_MMA) mma_role<C>(sm, tmem, p, rg, lo, hi);
+      if (warp == C::W_TMA && lane == 0) load_role<C>(sm, &tmQ, &tmK, &tmV, p, n, h, vcol0, r0, rg, lo, hi);
     }
     __syncwarp();
   }

@@ -62,7 +62,7 @@ struct KernelParams {
   // every CTA walks res_rows rows of one batch element, res_chunks CTAs cover its evo_inner rows
   int pair_h, pair_b;
   int res_rows, res_chunks;
-  int res_slots;  // K/V slots of this launch's ring (the bias tiles lie behind them)
+  int res_slots;  // slots (one tile each) of each stage's K/V ring; the bias tiles lie behind the rings
   // masks
   int causal;                // document mask: also require j <= i
   int window;                // sliding window (keys i-window .. i)
