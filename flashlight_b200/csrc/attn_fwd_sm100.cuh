@@ -35,10 +35,10 @@
 
 namespace flb {
 
-template <int E_, int EV_, int SCORE_, int MASK_, bool DIFF_, int STAGES_ = 2>
+template <int E_, int EV_, int SCORE_, int MASK_, int DIFF_, int STAGES_ = 2>
 struct AttnCfg {
   static constexpr int E = E_, EV = EV_, SCORE = SCORE_, MASK = MASK_;
-  static constexpr bool DIFF = DIFF_;
+  static constexpr bool DIFF = DIFF_ != 0;  // differential attention: 1 = P as one bf16 term, 2 = as two
   // Query tiles per CTA.  Two: 512 threads, all of tensor memory, one CTA per SM, the stages share
   // every K/V tile.  One: 256 threads, half of tensor memory and of shared memory, two CTAs per
   // SM that run independently, so one CTA's set-up and epilogue hide behind the other's tiles
@@ -53,18 +53,14 @@ struct AttnCfg {
   // Differential attention subtracts two nearly equal softmax averages and then normalises the
   // result to unit RMS, which amplifies the rounding of P to bf16 to about the size of the
   // tolerance.  There P is written as two bf16 terms (hi + lo) and the PV product runs on both.
-  static constexpr bool SPLIT_P = DIFF_;
+  // Without the normalisation one term is an order of magnitude inside the tolerance (mean-abs
+  // 1.0e-4), and the second would cost 8 of 20 MMA steps per tile and the tile tried with the running
+  // maximum: the kernel is built both ways.
+  static constexpr bool SPLIT_P = DIFF_ == 2;
   // ALiBi's bias grows along the keys, so a walk from the first key tile up would raise every
   // row maximum tile after tile and rescale the accumulator each time.  Walking the tiles from
   // the last one down meets the largest bias first; the result does not depend on the order.
   static constexpr bool REVERSE = SCORE_ == SCORE_ALIBI;
-  // Let the PV product start on the first 64 keys of P while the softmax warps still work on the
-  // other 64.  It pays where the softmax of a tile is long (softcap: two transcendentals per
-  // score); elsewhere the extra hand-off costs more than the overlap brings.
-#ifndef FLB_SOFTCAP_EARLY_PV
-#define FLB_SOFTCAP_EARLY_PV 1
-#endif
-  static constexpr bool EARLY_PV = FLB_SOFTCAP_EARLY_PV && SCORE_ == SCORE_SOFTCAP;
   // back-to-back product O = f(Q K^T * scale) V: no softmax; KT: K arrives as [E][S], keys contiguous
   // Resident pair bias: the CTA keeps one (head, query tile), loads that tile's pair-bias columns
   // once and walks a range of rows (MSA rows of Evoformer attention) that all add the same bias;
@@ -112,15 +108,9 @@ struct AttnCfg {
   // waits for the tensor core (narrow heads are bound by the exponentials, not by the MMAs).
   static constexpr bool SEP_P = !DIFF_ && EV_ <= 64;
   // softmax tries a tile with the running maximum first and looks for a new one only when the
-  // tile's row sums say that it was too small (needs the whole P tile in registers at once)
-#ifndef FLB_SPECULATE
-#define FLB_SPECULATE 1
-#endif
-#ifndef FLB_SPECULATE_SEP
-#define FLB_SPECULATE_SEP 1
-#endif
-  static constexpr bool SPECULATE = FLB_SPECULATE && !DIFF_ && !EARLY_PV && MASK_ != MASK_DOCUMENT &&
-                                    !B2B && (FLB_SPECULATE_SEP || !SEP_P);
+  // tile's row sums say that it was too small (needs the whole P tile in registers at once, so
+  // not where P has two terms; the document mask measured 3 % slower with it)
+  static constexpr bool SPECULATE = MASK_ != MASK_DOCUMENT && !B2B && !SPLIT_P;
   static constexpr int COL_P0 = STAGES == 2 ? 384 : 128 + EV, COL_P1 = 448;
   static_assert(!SEP_P || COL_P0 + 64 <= TMEM_COLS, "P columns do not fit");
   static_assert(E % 16 == 0 && EV % 16 == 0, "head dims must be multiples of 16");
@@ -134,14 +124,14 @@ enum : int {
   BAR_S_FULL = 2,      // +s   MMA -> softmax: S tile written
   BAR_P_FULL = 4,      // +s   softmax -> MMA: P tile written
   BAR_PV_DONE = 6,     // +s   MMA -> softmax / epilogue: O accumulated
-  BAR_P_HALF = 8,      // +s   softmax -> MMA: first 64 keys of the P tile written
+  BAR_P_HALF = 8,      // +s   (free; the resident-bias kernel uses the pair as Q_EMPTY)
   BAR_SCALE_FULL = 10, // +s   softmax -> epilogue: final row sums published
   BAR_O_STAGED = 12,   // +s   epilogue threads -> storing thread: output tile written to shared memory
   BAR_KV_FULL = 14,    // +slot
   BAR_KV_EMPTY = 22,   // +slot
   BAR_S_FREE = 30,     // +s   softmax -> MMA: S tile read into registers (only with SEP_P)
   BAR_COUNT = 48,
-  // resident-bias kernel: it uses neither P_HALF nor O_STAGED, and each stage has a K/V ring, a
+  // resident-bias kernel: it does not use O_STAGED, and each stage has a K/V ring, a
   // producer and an MMA warp of its own (up to seven slots per stage)
   BAR_Q_EMPTY = BAR_P_HALF,    // +s   MMA -> producer: the row's last QK product has read Q
   BAR_O_FREE = BAR_O_STAGED,   // +s   epilogue -> MMA / softmax: the row's accumulator and row sums are read
@@ -518,12 +508,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
           if (have_v && u - 1 >= first[s] && u - 1 < first[s] + cnt[s]) {
             const int it = u - 1 - first[s];
             const uint32_t tA = C::SEP_P ? tP[s] : tS[s];  // where the softmax warps put P
-            // the product starts on the first 64 keys while the softmax warps finish the rest
-            if constexpr (C::EARLY_PV) {
-              FLB_WAIT(sm, BAR_P_HALF + s, it & 1);
-            } else {
-              FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
-            }
+            FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
             tc_fence_after();
             if (it > 0) umma_ts_c<1>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
             else umma_ts_c<0>(leader, tO[s], tA, v_lo, v_hi, idesc_pv);
@@ -535,10 +520,6 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
               for (int k = 0; k < kTileN / 32; ++k)
                 umma_ts_c<1>(leader, tO[s], tA + 64 + k * 8, v_lo + ((k * 16 * C::VBOX * 2) >> 4), v_hi,
                              idesc_pv);
-            }
-            if constexpr (C::EARLY_PV) {
-              FLB_WAIT(sm, BAR_P_FULL + s, it & 1);
-              tc_fence_after();
             }
 #pragma unroll
             for (int k = kTileN / 32; k < kTileN / 16; ++k)
@@ -632,27 +613,15 @@ FLB_DEV float2 exp2_poly2(float2 x) {
 
 // Register budgets after the roles split (setmaxnreg; 8 softmax warps, 4 epilogue warps, 4 warps
 // around the MMA and TMA issuers: 256 * softmax + 128 * epilogue + 128 * issue <= 65536)
-#ifndef FLB_REGS_SOFTMAX
-#define FLB_REGS_SOFTMAX 192
-#define FLB_REGS_EPILOGUE 64
-#define FLB_REGS_ISSUE 64
-#endif
+constexpr int kRegsSoftmax = 192, kRegsEpilogue = 64, kRegsIssue = 64;
 // one query tile per CTA: 256 threads start with 128 registers each (two CTAs per SM); four
 // softmax warps and the warpgroup around the two issuing warps: 128 * softmax + 128 * issue <= 32768
-#ifndef FLB_REGS_SOFTMAX1
-#define FLB_REGS_SOFTMAX1 200
-#define FLB_REGS_ISSUE1 56
-#endif
+constexpr int kRegsSoftmax1 = 200, kRegsIssue1 = 56;
 
-// Of every FLB_POLY_PERIOD column pairs, FLB_POLY_COUNT go through exp2_poly2, the rest through
-// ex2.approx.  One pair in four measured best (a third or more is slower than none); the
-// differential variant, which rounds P twice, keeps all pairs on ex2.approx.
-#ifndef FLB_POLY_PERIOD
-#define FLB_POLY_PERIOD 4
-#endif
-#ifndef FLB_POLY_COUNT
-#define FLB_POLY_COUNT 1
-#endif
+// Of every kPolyPeriod column pairs, kPolyCount go through exp2_poly2, the rest through ex2.approx.
+// One pair in four measured best (a third or more is slower than none).  A P of two bf16 terms
+// (differential attention with the RMS normalisation) keeps all pairs on ex2.approx.
+constexpr int kPolyPeriod = 4, kPolyCount = 1;
 
 template <class C>
 FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p, int s, int n,
@@ -953,7 +922,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
             x = __ffma2_rn(s2, kmul2, nmk2);
           }
           float2 pr;
-          if ((idx >> 1) % FLB_POLY_PERIOD < FLB_POLY_COUNT) {
+          if ((idx >> 1) % kPolyPeriod < kPolyCount) {
             pr = exp2_poly2(x);
           } else {
             pr.x = ex2(x.x);
@@ -1050,7 +1019,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
         const int idx = chunk * 32 + c;
         const float2 x = __ffma2_rn(make_float2(u2f(v[idx]), u2f(v[idx + 1])), kmul2, nmk2);
         float2 pr;
-        if (!C::SPLIT_P && (c >> 1) % FLB_POLY_PERIOD < FLB_POLY_COUNT) {
+        if (!C::SPLIT_P && (c >> 1) % kPolyPeriod < kPolyCount) {
           pr = exp2_poly2(x);
         } else {
           pr.x = ex2(x.x);
@@ -1068,12 +1037,6 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
       }
       tmem_st16(tPs + chunk * 16, pk);   // stores overlap the next chunk's arithmetic
       if constexpr (C::SPLIT_P) tmem_st16(tPs + 64 + chunk * 16, pk_lo);
-      if (C::EARLY_PV && chunk == 1) {
-        // the first 64 keys of P are in place: the PV product may start on them
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(sm.bar(BAR_P_HALF + s));
-      }
     }
     l += (suma.x + suma.y) + (sumb.x + sumb.y);
     }  // !done
@@ -1464,7 +1427,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     sm.ctl()->abort = 1;
 
   if (warp < C::W_SOFTMAX_END) {
-    reg_inc<C::STAGES == 2 ? FLB_REGS_SOFTMAX : FLB_REGS_SOFTMAX1>();
+    reg_inc<C::STAGES == 2 ? kRegsSoftmax : kRegsSoftmax1>();
     const int s = warp >> 2;
     if constexpr (C::ROWLOOP) {
       for (int ri = 0; ri < rw.items(s) && !sm.ctl()->abort; ++ri)
@@ -1476,11 +1439,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // one query tile per CTA: its softmax warps also write the result
     if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else if (C::STAGES == 2 && warp < 12) {
-    reg_dec<FLB_REGS_EPILOGUE>();
+    reg_dec<kRegsEpilogue>();
     if constexpr (C::ROWLOOP) epilogue_role_rows<C>(sm, tmem, &tmO, p, rb_h, r0[0], rw);
     else epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else {
-    reg_dec<C::STAGES == 2 ? FLB_REGS_ISSUE : FLB_REGS_ISSUE1>();
+    reg_dec<C::STAGES == 2 ? kRegsIssue : kRegsIssue1>();
     if constexpr (C::ROWLOOP) {
       const int s = (warp - C::W_MMA) >> 1;  // warps 12, 13: stage 0; 14, 15: stage 1
       if (rw.items(s) > 0) {

@@ -1,8 +1,8 @@
 // head dim 128: sliding window, prefix-LM, document mask, additive bias
 #include "attn_launch_impl.cuh"
 namespace flb {
-FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_SLIDING, false, 2)
-FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_PREFIX, false, 2)
-FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_DOCUMENT, false, 2)
-FLB_INSTANTIATE(128, 128, SCORE_BIAS, MASK_NONE, false, 2)
+FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_SLIDING, 0, 2)
+FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_PREFIX, 0, 2)
+FLB_INSTANTIATE(128, 128, SCORE_NONE, MASK_DOCUMENT, 0, 2)
+FLB_INSTANTIATE(128, 128, SCORE_BIAS, MASK_NONE, 0, 2)
 }

@@ -1,8 +1,8 @@
 // one query tile per CTA, head dim 64: sliding window, prefix-LM, document mask, additive bias
 #include "attn_launch_impl.cuh"
 namespace flb {
-FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_SLIDING, false, 1)
-FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_PREFIX, false, 1)
-FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_DOCUMENT, false, 1)
-FLB_INSTANTIATE(64, 64, SCORE_BIAS, MASK_NONE, false, 1)
+FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_SLIDING, 0, 1)
+FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_PREFIX, 0, 1)
+FLB_INSTANTIATE(64, 64, SCORE_NONE, MASK_DOCUMENT, 0, 1)
+FLB_INSTANTIATE(64, 64, SCORE_BIAS, MASK_NONE, 0, 1)
 }

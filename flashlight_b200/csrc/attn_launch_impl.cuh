@@ -5,7 +5,7 @@
 
 namespace flb {
 
-template <int E, int EV, int SCORE, int MASK, bool DIFF, int STAGES>
+template <int E, int EV, int SCORE, int MASK, int DIFF, int STAGES>
 cudaError_t launch_attn(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
                         const CUtensorMap& tmO, const CUtensorMap& tmB, const KernelParams& p, int grid,
                         int cluster,

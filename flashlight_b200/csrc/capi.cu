@@ -308,14 +308,14 @@ int build_block_map(const flb200_attn_params* p, cudaStream_t stream) {
   return FLB200_OK;
 }
 
-template <int E, int EV, bool DIFF, int STAGES>
+template <int E, int EV, int DIFF, int STAGES>
 cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUtensorMap& b,
                           const CUtensorMap& c, const CUtensorMap& o, const KernelParams& kp,
                           int grid, int cluster, cudaStream_t st) {
 #define FLB_CASE(SC, MK)          \
   if (score == SC && mask == MK)  \
     return launch_attn<E, EV, SC, MK, DIFF, STAGES>(a, b, c, o, a, kp, grid, cluster, st);
-  if constexpr (DIFF) {
+  if constexpr (DIFF != 0) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
   } else if constexpr (E == 32) {
@@ -553,20 +553,29 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
   cudaError_t e = cudaErrorInvalidValue;
   const int sc = kscore, mk = p->mask;
   if (p->diff) {
-    if (width == 128) e = dispatch_mods<128, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else if (width == 64) e = dispatch_mods<64, 128, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else e = dispatch_mods<32, 64, true, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    // The RMS normalisation scales the small difference of two softmax averages up to unit size, and
+    // the rounding of P with it: P then carries a second bf16 term.  FLB200_DIFF_SPLIT_P=0|1 forces
+    // the choice (for measuring what the second term buys).
+    bool split = p->diff_rms_norm != 0;
+    if (const char* e2 = std::getenv("FLB200_DIFF_SPLIT_P")) split = std::atoi(e2) != 0;
+#define FLB_DIFF(E, EV)                                                                                     \
+  (split ? dispatch_mods<E, EV, 2, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream)               \
+         : dispatch_mods<E, EV, 1, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream))
+    if (width == 128) e = FLB_DIFF(128, 128);
+    else if (width == 64) e = FLB_DIFF(64, 128);
+    else e = FLB_DIFF(32, 64);
+#undef FLB_DIFF
   } else if (res.use) {
-    if (width == 64) e = launch_attn<64, 64, SCORE_BIAS_RES, MASK_NONE, false, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
-    else e = launch_attn<32, 32, SCORE_BIAS_RES, MASK_NONE, false, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
+    if (width == 64) e = launch_attn<64, 64, SCORE_BIAS_RES, MASK_NONE, 0, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
+    else e = launch_attn<32, 32, SCORE_BIAS_RES, MASK_NONE, 0, 2>(tmQ, tmK, tmV, tmO, tmB, kp, grid, 1, stream);
   } else if (stages == 2) {
-    if (width == 128) e = dispatch_mods<128, 128, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else if (width == 64) e = dispatch_mods<64, 64, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else e = dispatch_mods<32, 32, false, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    if (width == 128) e = dispatch_mods<128, 128, 0, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, 0, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else e = dispatch_mods<32, 32, 0, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   } else {
-    if (width == 128) e = dispatch_mods<128, 128, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else if (width == 64) e = dispatch_mods<64, 64, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
-    else e = dispatch_mods<32, 32, false, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    if (width == 128) e = dispatch_mods<128, 128, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 64) e = dispatch_mods<64, 64, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else e = dispatch_mods<32, 32, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   }
   if (e != cudaSuccess) return FLB200_E_LAUNCH;
   g_launches.fetch_add(1, std::memory_order_relaxed);
