@@ -47,10 +47,13 @@ UNIT = "TFLOP/s"
 L2_BYTES = 126 * 1024 * 1024
 
 # DRAM bytes (read + write) per launch of the attention kernel at the full size of the workload,
-# from a profiler capture of `dram__bytes_read.sum + dram__bytes_write.sum`; None where no
-# full-size capture exists (a capture of a smaller batch does not extrapolate: its working set
-# sits in L2).
-NCU_TRAFFIC_BYTES = {}
+# from profiler captures of `dram__bytes_read.sum + dram__bytes_write.sum` on the workloads as they
+# stand here (a capture of a smaller batch does not extrapolate: its working set sits in L2);
+# None where no full-size capture exists.
+NCU_TRAFFIC_BYTES = {
+    "causal_gqa": 967e6, "softcap_causal": 718e6, "sliding_window": 782e6, "document_causal": 538e6,
+    "evoformer": 190e6, "diff_attn": 407e6,
+}
 
 
 def parse_args(argv=None):
@@ -469,7 +472,7 @@ def main():
             flashlight_b200.check_status()
             ms = ms_b2b / reps
             row = {"ms": ms, "ms_median_per_launch": statistics.median(pl), "tflops": fl_w / (ms * 1e-3) / 1e12,
-                   "effective_flops": fl_w, "hbm_bytes": by_w, "l2": note}
+                   "effective_flops": fl_w, "hbm_bytes": by_w, "traffic": NCU_TRAFFIC_BYTES.get(name), "l2": note}
             row.update(roof(fl_w, by_w, ms, peak_tf, peak_hbm))
             if wl.variant == "document":
                 # the block map is cached per document_id tensor: also a step that rebuilds it
