@@ -81,7 +81,12 @@ struct AttnCfg {
   static constexpr int V_HEAD_BYTES = 128 * EV * 2;
   static constexpr int V_BYTES = V_HEAD_BYTES;
   static constexpr int SLOT_BYTES = K_BYTES > V_BYTES ? K_BYTES : V_BYTES;
-  static constexpr int SMEM_BUDGET = STAGES == 2 ? 224 * 1024 : 110 * 1024;
+  // Tensor-memory columns one CTA needs.  Two stages: all 512.  One stage: the score tile, the
+  // accumulator and, for narrow heads, P: 256 columns (two CTAs per SM) up to value heads of 128,
+  // 512 above (heads up to 256: one CTA per SM, which then also gets the whole shared memory).
+  static constexpr bool WIDE = E_ > 128 || EV_ > 128;
+  static_assert(!WIDE || STAGES_ == 1, "heads above 128 run one query tile per CTA");
+  static constexpr int SMEM_BUDGET = (STAGES == 2 || WIDE) ? 224 * 1024 : 110 * 1024;
   static constexpr int NSTAGE_FIT = (SMEM_BUDGET - STAGES * Q_BYTES) / SLOT_BYTES;
   // Resident bias: everything between the Q tiles / output staging and the barriers is shared by
   // the K/V ring and the bias tiles; the launch decides the split (KernelParams::res_slots): the
@@ -94,12 +99,12 @@ struct AttnCfg {
   // Shared memory also bounds how many CTAs share an SM, and with it their tensor-memory demand
   // (an allocation that does not fit would wait for a neighbour to leave): two-stage CTAs take
   // more than half of it (512 columns each), one-stage CTAs more than a third (256 columns each).
-  static constexpr int SMEM_FLOOR = STAGES == 2 ? 120 * 1024 : 80 * 1024;
+  static constexpr int SMEM_FLOOR = (STAGES == 2 || WIDE) ? 120 * 1024 : 80 * 1024;
   static constexpr int SMEM_BYTES = SMEM_USED < SMEM_FLOOR ? SMEM_FLOOR : SMEM_USED;
-  static_assert(STAGES == 2 || SMEM_BYTES <= 113 * 1024, "two one-stage CTAs must fit one SM");
+  static_assert(STAGES == 2 || WIDE || SMEM_BYTES <= 113 * 1024, "two one-stage CTAs must fit one SM");
   static constexpr uint32_t SWZ_K = KBOX == 64 ? kSwz128 : (KBOX == 32 ? kSwz64 : kSwz32);
   static constexpr uint32_t SWZ_V = VBOX == 64 ? kSwz128 : (VBOX == 32 ? kSwz64 : kSwz32);
-  static constexpr int TMEM_COLS = STAGES == 2 ? 512 : 256;
+  static constexpr int TMEM_COLS = (STAGES == 2 || WIDE) ? 512 : 256;
   static constexpr int COL_S0 = 0, COL_S1 = 128;
   static constexpr int COL_O0 = STAGES == 2 ? 256 : 128, COL_O1 = 256 + EV;
   // With value heads of 64 or less the accumulators leave 128 columns free: P gets columns of
@@ -114,7 +119,7 @@ struct AttnCfg {
   static constexpr int COL_P0 = STAGES == 2 ? 384 : 128 + EV, COL_P1 = 448;
   static_assert(!SEP_P || COL_P0 + 64 <= TMEM_COLS, "P columns do not fit");
   static_assert(E % 16 == 0 && EV % 16 == 0, "head dims must be multiples of 16");
-  static_assert(E <= 128 && EV <= 128, "head dims above 128 are not supported");
+  static_assert(E <= 256 && EV <= 256, "head dims above 256 are not supported");
   static_assert(NSTAGE >= 2, "ring too small");
 };
 

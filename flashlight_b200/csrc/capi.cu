@@ -70,7 +70,10 @@ MapLayout map_layout(const flb200_attn_params* p) {
 // to q.k, and the value columns beyond Ev are clipped by the output store).
 bool kernel_built(int D, int score, int mask) {
   if (score == SCORE_BIAS_RES) return mask == MASK_NONE && (D == 32 || D == 64);
-  if (score == SCORE_B2B || score == SCORE_B2BT) return mask == MASK_NONE && (D == 32 || D == 64 || D == 128);
+  if (score == SCORE_B2B || score == SCORE_B2BT)
+    return mask == MASK_NONE && (D == 32 || D == 64 || D == 128 || D == 256);
+  // heads above 128 (up to 256): plain and causal attention and the product chain, one stage per CTA
+  if (D == 256) return score == SCORE_NONE && (mask == MASK_NONE || mask == MASK_CAUSAL);
   if (D == 32)
     return (score == SCORE_NONE && (mask == MASK_NONE || mask == MASK_CAUSAL)) ||
            (score == SCORE_BIAS && mask == MASK_NONE);
@@ -101,7 +104,7 @@ int kernel_width(int E, int EV, int score, int mask, int diff) {
     return 0;
   }
   const int need = E > EV ? E : EV;
-  for (int D : {32, 64, 128})
+  for (int D : {32, 64, 128, 256})
     if (D >= need && kernel_built(D, score, mask)) return D;
   return 0;
 }
@@ -211,6 +214,7 @@ int validate(const flb200_attn_params* p) {
 // windows, document masks, the softcap (whose tiles are long) and additive biases.
 // FLB200_STAGES=1|2 overrides the choice for tuning.
 int pick_stages(const flb200_attn_params* p) {
+  if (p->E > 128 || p->Ev > 128) return p->diff ? 2 : 1;  // wide heads have one-stage kernels only
   if (p->diff || p->product_chain) return 2;
   if (const char* e = std::getenv("FLB200_STAGES")) {
     const int v = std::atoi(e);
@@ -318,6 +322,11 @@ cudaError_t dispatch_mods(int score, int mask, const CUtensorMap& a, const CUten
   if constexpr (DIFF != 0) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
+  } else if constexpr (E == 256) {
+    FLB_CASE(SCORE_NONE, MASK_NONE)
+    FLB_CASE(SCORE_NONE, MASK_CAUSAL)
+    FLB_CASE(SCORE_B2B, MASK_NONE)
+    FLB_CASE(SCORE_B2BT, MASK_NONE)
   } else if constexpr (E == 32) {
     FLB_CASE(SCORE_NONE, MASK_NONE)
     FLB_CASE(SCORE_NONE, MASK_CAUSAL)
@@ -573,7 +582,8 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
     else if (width == 64) e = dispatch_mods<64, 64, 0, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else e = dispatch_mods<32, 32, 0, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   } else {
-    if (width == 128) e = dispatch_mods<128, 128, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    if (width == 256) e = dispatch_mods<256, 256, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 128) e = dispatch_mods<128, 128, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else if (width == 64) e = dispatch_mods<64, 64, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
     else e = dispatch_mods<32, 32, 0, 1>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
   }

@@ -70,8 +70,9 @@ def test_strerror_distinct(lib):
     (dict(mask=_lib.MASK_SLIDING, window=-1), _lib.E_BAD_ARG),
     (dict(mask=_lib.MASK_SLIDING, window=8, S=128), _lib.E_BAD_ARG),  # L != S
     (dict(mask=_lib.MASK_DOCUMENT), _lib.E_BAD_ARG),                 # no ids
-    (dict(E=256, Ev=256), _lib.E_UNSUPPORTED),
-    (dict(E=136, Ev=64), _lib.E_UNSUPPORTED),
+    (dict(E=264, Ev=264), _lib.E_UNSUPPORTED),
+    (dict(E=64, Ev=320), _lib.E_UNSUPPORTED),
+    (dict(E=256, Ev=256, mask=_lib.MASK_SLIDING, window=8), _lib.E_UNSUPPORTED),   # wide heads: plain and causal only
     (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE + 4), _lib.E_MISALIGNED),
     (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE, N=70000), _lib.E_UNSUPPORTED),
     (dict(mask=_lib.MASK_DOCUMENT, document_id=FAKE, doc_stride_n=8), _lib.E_BAD_ARG),   # rows of L ids overlap
@@ -87,7 +88,8 @@ def test_validate_rejects(lib, over, code):
 
 @pytest.mark.parametrize("E,Ev", [(96, 96), (128, 64), (64, 128), (48, 16), (8, 8), (120, 128)])
 def test_narrow_and_unequal_head_dims_run_on_the_next_wider_kernel(lib, E, Ev):
-    """Any head dims up to 128 are served: the tensor maps zero-fill the missing feature columns."""
+    """Any head dims up to 128 are served by every variant: the tensor maps zero-fill the missing
+    feature columns."""
     p = good(E=E, Ev=Ev)
     for name, w in (("q_stride", E), ("k_stride", E), ("v_stride", Ev), ("o_stride", Ev)):
         arr = getattr(p, name)
@@ -96,6 +98,19 @@ def test_narrow_and_unequal_head_dims_run_on_the_next_wider_kernel(lib, E, Ev):
     # ALiBi has no 32-wide kernel of its own: it runs on the 64-wide one
     p.score_mod, p.alibi_heads = _lib.SCORE_ALIBI, p.Hq
     assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
+
+
+@pytest.mark.parametrize("E,Ev", [(256, 256), (192, 192), (136, 64), (64, 256)])
+def test_heads_up_to_256_for_plain_and_causal_attention(lib, E, Ev):
+    p = good(E=E, Ev=Ev)
+    for name, w in (("q_stride", E), ("k_stride", E), ("v_stride", Ev), ("o_stride", Ev)):
+        arr = getattr(p, name)
+        arr[2], arr[1], arr[0] = w, w * 256, w * 256 * p.Hq
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
+    p.mask = _lib.MASK_CAUSAL
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.OK
+    p.score_mod, p.alibi_heads = _lib.SCORE_ALIBI, p.Hq
+    assert lib.flb200_attn_validate(C.byref(p)) == _lib.E_UNSUPPORTED
 
 
 def test_stride_alignment(lib):

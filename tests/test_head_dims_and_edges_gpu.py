@@ -34,6 +34,16 @@ def test_any_head_dim_up_to_128(E, Ev, S):
           ao.alibi(q, k, v, nheads=4, enable_gqa=True), (E, Ev))
 
 
+@pytest.mark.parametrize("E,Ev", [(256, 256), (192, 192), (136, 64), (64, 256), (200, 160)])
+@pytest.mark.parametrize("S", [200, 1000])
+def test_head_dims_up_to_256(E, Ev, S):
+    """Heads above 128 (the reference takes any width up to 256 as a one-shot reduction range,
+    monkeypatch/fusion/_common.py:4) run plain and causal attention with one query tile per CTA."""
+    q, k, v = rnd((2, 4, S, E), 31), rnd((2, 2, S, E), 32), rnd((2, 2, S, Ev), 33)
+    check(av.attention_pytorch(q, k, v, enable_gqa=True), ao.vanilla(q, k, v, enable_gqa=True), (E, Ev))
+    check(av.attention_pytorch_causal(q, k, v, enable_gqa=True), ao.causal(q, k, v, enable_gqa=True), (E, Ev))
+
+
 def test_diff_attention_with_narrow_heads():
     q, k, v = rnd((1, 4, 300, 48), 4), rnd((1, 4, 300, 48), 5), rnd((1, 2, 300, 96), 6)
     check(av.diffattn(q, k, v, lambda_full=0.5), ao.diffattn(q, k, v, lambda_full=0.5))

@@ -341,7 +341,7 @@ def test_pinned_host_batches_are_pipelined_and_identical():
 
 
 def test_unsupported_raises_instead_of_falling_back():
-    q = rnd((1, 2, 128, 136), 55)                     # head dims above 128 have no kernel
+    q = rnd((1, 2, 128, 264), 55)                     # head dims above 256 have no kernel
     with pytest.raises(NotImplementedError):
         av.attention_pytorch(q, q, q)
     q = rnd((1, 2, 128, 64), 55)

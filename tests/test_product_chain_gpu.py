@@ -31,20 +31,21 @@ def normal(shape, seed):
     return torch.randn(*shape, generator=g, device="cuda").to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("batch,n_ctx,head_dim", [(2, 1024, 128), (1, 2048, 64), (2, 64, 32)])
+@pytest.mark.parametrize("batch,n_ctx,head_dim", [(2, 1024, 128), (1, 2048, 64), (4, 512, 256), (2, 64, 32)])
 def test_reference_test_shapes(batch, n_ctx, head_dim):
     q, k, v = uniform((batch, n_ctx, head_dim), 1), uniform((batch, head_dim, n_ctx), 2), uniform((batch, n_ctx, head_dim), 3)
     close(fused_bmm(q, k, v), ao.product_chain(q, k, v))
 
 
-def test_width_256_has_no_kernel():
-    q, k, v = uniform((1, 256, 256), 1), uniform((1, 256, 256), 2), uniform((1, 256, 256), 3)
+def test_widths_above_256_have_no_kernel():
+    q, k, v = uniform((1, 256, 264), 1), uniform((1, 264, 256), 2), uniform((1, 256, 264), 3)
     with pytest.raises(NotImplementedError):
         fused_bmm(q, k, v)
 
 
 @pytest.mark.parametrize("pointwise", ["identity", "relu", "tanh", "sigmoid"])
-@pytest.mark.parametrize("M,N,O,P", [(300, 128, 520, 128), (128, 64, 128, 64), (1000, 32, 77, 32), (257, 96, 640, 48)])
+@pytest.mark.parametrize("M,N,O,P", [(300, 128, 520, 128), (128, 64, 128, 64), (1000, 32, 77, 32), (257, 96, 640, 48),
+                                     (300, 200, 333, 256)])
 def test_pointwise_middles_and_odd_shapes(pointwise, M, N, O, P):
     a, b, c = normal((3, M, N), 4), normal((3, N, O), 5), normal((3, O, P), 6)
     scale = N ** -0.5
