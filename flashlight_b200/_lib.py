@@ -75,6 +75,29 @@ class AttnParams(C.Structure):
     ]
 
 
+class AttnBwdParams(C.Structure):
+    """Mirror of `flb200_attn_bwd_params`."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("N", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("L", C.c_int32), ("S", C.c_int32), ("E", C.c_int32),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("dout", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("o_stride", C.c_int64 * 3), ("do_stride", C.c_int64 * 3),
+        ("dq_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3), ("dv_stride", C.c_int64 * 3),
+        ("lse_stride", C.c_int64 * 2),
+        ("scale", C.c_float),
+        ("causal", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("status", C.c_void_p),
+        ("status_host", C.c_void_p),
+        ("wait_limit_us", C.c_uint32),
+    ]
+
+
 EXPORTS = (
     "flb200_abi_version",
     "flb200_strerror",
@@ -84,6 +107,8 @@ EXPORTS = (
     "flb200_attn_fwd",
     "flb200_attn_fwd_noalloc",
     "flb200_selftest_wait_timeout",
+    "flb200_attn_bwd_workspace_bytes",
+    "flb200_attn_bwd",
     "flb200_decode_status",
     "flb200_launch_count",
 )
@@ -118,6 +143,11 @@ def load() -> C.CDLL:
     lib.flb200_attn_fwd_noalloc.argtypes = [P, C.c_void_p]
     lib.flb200_selftest_wait_timeout.restype = C.c_int
     lib.flb200_selftest_wait_timeout.argtypes = [P, C.c_void_p]
+    PB = C.POINTER(AttnBwdParams)
+    lib.flb200_attn_bwd_workspace_bytes.restype = C.c_size_t
+    lib.flb200_attn_bwd_workspace_bytes.argtypes = [PB]
+    lib.flb200_attn_bwd.restype = C.c_int
+    lib.flb200_attn_bwd.argtypes = [PB, C.c_void_p]
     lib.flb200_decode_status.restype = C.c_int
     lib.flb200_decode_status.argtypes = [C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.flb200_launch_count.restype = C.c_uint64

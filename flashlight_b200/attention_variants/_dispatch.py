@@ -110,6 +110,19 @@ def run(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, *, scale: f
             out = out.view(out.size(0), Hkv, Hq // Hkv, out.size(2), out.size(3))
         return out
     q, k, v = _dev(query, device), _dev(key, device), _dev(value, device)
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        # gradients: plain and causal attention have backward kernels (the reference stubs its backward)
+        plain = (score_mod == _lib.SCORE_NONE and mask in (_lib.MASK_NONE, _lib.MASK_CAUSAL) and not diff
+                 and b0 is None and b1 is None and not rows_major_out and home.type == "cuda"
+                 and q.size(3) == v.size(3) and q.size(3) <= 128)
+        if not plain:
+            raise NotImplementedError("flashlight_b200: gradients are implemented for plain and causal attention "
+                                      "(equal q/k and v head dims up to 128); no other variant has a backward kernel")
+        from ..ops import attention_with_grad
+        out = attention_with_grad(q, k, v, float(scale), mask == _lib.MASK_CAUSAL)
+        if enable_gqa and gqa_5d:
+            out = out.view(out.size(0), Hkv, Hq // Hkv, out.size(2), out.size(3))
+        return out
     out = attn_fwd(q, k, v, float(scale), int(score_mod), int(alibi_heads), int(alibi_head0), float(softcap),
                    int(mask), bool(causal), int(window), _dev(prefix_len, device),
                    int(prefix_scalar), _dev(document_id, device), b0, b1, int(bias_inner),

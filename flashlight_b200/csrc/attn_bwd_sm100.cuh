@@ -1,0 +1,495 @@
+// Attention backward for sm_100a: dQ, dK, dV of softmax(Q K^T * scale [+ causal mask]) V from the
+// forward's inputs, its output, its row-wise log-sum-exp and the output's gradient.
+//
+// Three kernels, none of which needs an atomic or a transpose in memory:
+//
+//   attn_bwd_delta_kernel   delta[i] = sum_d dO[i][d] * O[i][d]  (fp32, one warp per query row)
+//
+//   attn_bwd_dq_kernel      one CTA per (batch, query head, 128-row query tile); walks the key tiles:
+//                             S = Q K^T, dP = dO V^T            (tcgen05 SS products into tensor memory)
+//                             P = exp2(S * scale_log2 - lse2),  dS = P * (dP - delta) * scale
+//                             dQ += dS K                         (dS read from tensor memory)
+//
+//   attn_bwd_dkv_kernel     one CTA per (batch, kv head, 128-key tile); walks the query tiles of every
+//                           query head of the group, with the roles of rows and columns swapped
+//                           (tensor-memory lanes are keys):
+//                             S^T = K Q^T, dP^T = V dO^T;  P^T, dS^T as above (lse2, delta per column)
+//                             dV += P^T dO,  dK += dS^T Q
+//
+// The score products are recomputed in both kernels (7 tile products per pair of tiles instead of 5);
+// in exchange every accumulator stays in one CTA's tensor memory from start to finish.
+// Tensor memory: S 128 + dP 128 + accumulators (D for dQ; 2 D for dV, dK) <= 512 columns, one CTA per
+// SM.  256 threads: warps 0-3 pointwise pass and epilogue (one thread per tensor-memory lane), warp 4
+// MMA issue, warp 5 TMA producer.  All waits are bounded as in the forward kernel.
+#pragma once
+#include <cuda.h>
+#include <math_constants.h>
+
+#include "ptx.cuh"
+
+namespace flb {
+
+struct BwdParams {
+  int N, Hq, Hkv, L, S, G;
+  float scale, scale_log2;
+  int causal;
+  const float* lse;  // [N][Hq][L], natural log
+  int64_t lse_sn, lse_sh;
+  float* delta;      // [N][Hq][Lp], Lp = L rounded up to 128
+  int Lp;
+  int* status;
+  int* status_host;
+  uint32_t wait_limit_us;
+};
+
+enum : int {
+  BB_RES_FULL = 0,  // the CTA's resident tiles (Q, dO or K, V) have landed
+  BB_SP_FULL = 1,   // MMA -> pointwise: both score tiles written
+  BB_DS_FULL = 2,   // pointwise -> MMA: P / dS written back (128 arrivals)
+  BB_ACC_DONE = 3,  // MMA -> epilogue: accumulators final
+  BB_RING_FULL = 4,   // +slot
+  BB_RING_EMPTY = 8,  // +slot
+  BB_COUNT = 12
+};
+
+template <int D_>
+struct BwdCfg {
+  static constexpr int D = D_;
+  static_assert(D == 64 || D == 128, "backward kernels are built for head dims 64 and 128");
+  static constexpr int NB = D / 64;                 // 64-column boxes per tile
+  static constexpr int BOX_BYTES = 128 * 64 * 2;    // 16 KB
+  static constexpr int TILE_BYTES = 128 * D * 2;
+  static constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // a ring slot holds the step's two streamed tiles
+  static constexpr int NSLOT = D == 128 ? 2 : 4;
+  static constexpr int VEC_BYTES = 2 * 2 * 128 * 4;  // lse2 / delta of the step's 128 queries, two buffers
+  static constexpr int AUX_BYTES = 1024;
+  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSLOT * SLOT_BYTES + VEC_BYTES + AUX_BYTES;
+  static_assert(SMEM_BYTES > 120 * 1024, "one CTA per SM: each takes all of tensor memory");
+};
+
+template <class C>
+struct BwdSmem {
+  uint8_t* base;
+  FLB_DEV uint8_t* res(int i) const { return base + i * C::TILE_BYTES; }  // resident tile 0 / 1
+  FLB_DEV uint8_t* slot(int s, int i) const { return base + 2 * C::TILE_BYTES + s * C::SLOT_BYTES + i * C::TILE_BYTES; }
+  FLB_DEV float* vec(int buf, int which) const {
+    return reinterpret_cast<float*>(base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES) + (buf * 2 + which) * 128;
+  }
+  FLB_DEV uint8_t* aux() const { return base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES + C::VEC_BYTES; }
+  FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
+  FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 128); }
+  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 132); }
+};
+
+#define FLB_BWAIT(sm, id, parity)                                 \
+  do {                                                            \
+    if (!mbar_wait((sm).bar(id), (parity), (sm).ctl())) {         \
+      atomicCAS(&(sm).ctl()->fail_bar, -1, 64 + (id));            \
+      return;                                                     \
+    }                                                             \
+  } while (0)
+
+// descriptor low/high words for a 128-row tile of 64-column, 128-byte-swizzled boxes
+//   K-major (rows are M or N, the features are the contraction axis)
+//   MN-major (rows are the contraction axis, the features are N)
+template <class C>
+struct BwdDesc {
+  static constexpr uint64_t kmaj = (static_cast<uint64_t>(1024 >> 4) << 32) | (1ull << 16) | (1ull << 46) |
+                                   (static_cast<uint64_t>(kSwz128) << 61);
+  static constexpr uint64_t mnmaj = (static_cast<uint64_t>(1024 >> 4) << 32) |
+                                    (static_cast<uint64_t>(C::BOX_BYTES >> 4) << 16) | (1ull << 46) |
+                                    (static_cast<uint64_t>(kSwz128) << 61);
+  static constexpr uint32_t k_hi = static_cast<uint32_t>(kmaj >> 32), k_lo = static_cast<uint32_t>(kmaj);
+  static constexpr uint32_t mn_hi = static_cast<uint32_t>(mnmaj >> 32), mn_lo = static_cast<uint32_t>(mnmaj);
+  FLB_DEV static uint32_t addr(const void* p) { return (smem_u32(p) & 0x3FFFFu) >> 4; }
+};
+
+// D[tmem 128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles in shared memory
+template <class C>
+FLB_DEV void bwd_mma_scores(uint32_t leader, uint32_t d_tmem, const void* a_tile, const void* b_tile) {
+  using Ds = BwdDesc<C>;
+  constexpr uint32_t idesc = make_idesc_bf16(128, 128, 0, 0);
+  const uint32_t a = Ds::k_lo + Ds::addr(a_tile), b = Ds::k_lo + Ds::addr(b_tile);
+  umma_ss_c<0>(leader, d_tmem, a, b, Ds::k_hi, idesc);
+#pragma unroll
+  for (int k = 1; k < C::D / 16; ++k) {
+    const int kk = k * 16;
+    const uint32_t off = ((kk / 64) * C::BOX_BYTES + (kk % 64) * 2) >> 4;
+    umma_ss_c<1>(leader, d_tmem, a + off, b + off, Ds::k_hi, idesc);
+  }
+}
+
+// D[tmem 128 x D] (+)= A[tmem 128 x 128, bf16] * B[128 x D], B an MN-major tile in shared memory
+template <class C>
+FLB_DEV void bwd_mma_acc(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, const void* b_tile, bool accumulate) {
+  using Ds = BwdDesc<C>;
+  constexpr uint32_t idesc = make_idesc_bf16(128, C::D, 0, 1);
+  const uint32_t b = Ds::mn_lo + Ds::addr(b_tile);
+  if (accumulate) umma_ts_c<1>(leader, d_tmem, a_tmem, b, Ds::mn_hi, idesc);
+  else umma_ts_c<0>(leader, d_tmem, a_tmem, b, Ds::mn_hi, idesc);
+#pragma unroll
+  for (int k = 1; k < 8; ++k)
+    umma_ts_c<1>(leader, d_tmem, a_tmem + k * 8, b + ((k * 16 * 128) >> 4), Ds::mn_hi, idesc);
+}
+
+template <class C>
+FLB_DEV void bwd_load_tile(uint8_t* dst, const CUtensorMap* tm, uint32_t bar, int row0, int head, int n) {
+#pragma unroll
+  for (int b = 0; b < C::NB; ++b)
+    tma_load_4d(smem_u32(dst) + b * C::BOX_BYTES, tm, bar, b * 64, row0, head, n);
+}
+
+// accumulator rows (fp32, `D` columns at `t_acc`) -> bf16 tile in shared memory in the layout of the
+// output tensor map (128-byte swizzled boxes of 64 columns)
+template <class C>
+FLB_DEV void bwd_stage_rows(uint32_t t_acc, uint8_t* tile, int row, float mul) {
+  const int sw = row & 7;
+#pragma unroll
+  for (int c0 = 0; c0 < C::D; c0 += 32) {
+    uint32_t o[32];
+    tmem_ld32_sync(t_acc + c0, o);
+#pragma unroll
+    for (int c = 0; c < 32; c += 8) {
+      uint4 w;
+      w.x = pack_bf16(__uint_as_float(o[c]) * mul, __uint_as_float(o[c + 1]) * mul);
+      w.y = pack_bf16(__uint_as_float(o[c + 2]) * mul, __uint_as_float(o[c + 3]) * mul);
+      w.z = pack_bf16(__uint_as_float(o[c + 4]) * mul, __uint_as_float(o[c + 5]) * mul);
+      w.w = pack_bf16(__uint_as_float(o[c + 6]) * mul, __uint_as_float(o[c + 7]) * mul);
+      const int col = c0 + c, box = col / 64, chunk = (col % 64) / 8;
+      *reinterpret_cast<uint4*>(tile + box * C::BOX_BYTES + row * 128 + ((chunk ^ sw) << 4)) = w;
+    }
+  }
+}
+
+template <class C>
+FLB_DEV void bwd_setup(const BwdSmem<C>& sm, const BwdParams& p, int warp, int lane) {
+  if (warp == 0) {
+    if (lane == 0) {
+      sm.ctl()->abort = 0;
+      sm.ctl()->fail_bar = -1;
+      sm.ctl()->limit_us = p.wait_limit_us;
+    }
+    if (lane < BB_COUNT) mbar_init(sm.bar(lane), lane == BB_DS_FULL ? 128 : 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(sm.tmem_base()), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 7 * 32 && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0)
+    sm.ctl()->abort = 1;
+}
+
+template <class C>
+FLB_DEV void bwd_exit(const BwdSmem<C>& sm, const BwdParams& p, int warp) {
+  tc_fence_before();
+  __syncthreads();
+  if (sm.ctl()->abort) {
+    for (int k = 0; k < 64; ++k) __nanosleep(20000);
+    if (threadIdx.x == 0 && p.status) {
+      const int word = (1 << 24) | ((sm.ctl()->fail_bar & 0xff) << 16) | (blockIdx.x & 0xffff);
+      if (atomicCAS(p.status, 0, word) == 0 && p.status_host != nullptr) {
+        *reinterpret_cast<volatile int*>(p.status_host) = word;
+        __threadfence_system();
+      }
+    }
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(*sm.tmem_base(), 512);
+}
+
+// ------------------------------------------------------------------------------------------
+// delta[n][h][i] = sum_d dO * O   (rows beyond L of the padded array: 0)
+// ------------------------------------------------------------------------------------------
+__global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                      int64_t o_sn, int64_t o_sh, int64_t o_sl, int64_t do_sn, int64_t do_sh,
+                                      int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);  // one warp per (n, h, i)
+  const int lane = threadIdx.x & 31;
+  const int i = row % Lp, nh = row / Lp, h = nh % Hq, n = nh / Hq;
+  float acc = 0.f;
+  if (i < L) {
+    const __nv_bfloat16* po = o + n * o_sn + h * o_sh + i * o_sl;
+    const __nv_bfloat16* pd = d_o + n * do_sn + h * do_sh + i * do_sl;
+    for (int d = lane; d < E; d += 32) acc = fmaf(__bfloat162float(po[d]), __bfloat162float(pd[d]), acc);
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[row] = acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// dQ
+// ------------------------------------------------------------------------------------------
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                   const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ BwdParams p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem<C> sm{reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023))};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.L + 127) / 128;
+  // heaviest (latest) query tiles first under the causal mask
+  const int qt = nq - 1 - static_cast<int>(blockIdx.x) / (p.N * p.Hq);
+  const int nh = static_cast<int>(blockIdx.x) % (p.N * p.Hq);
+  const int n = nh / p.Hq, h = nh % p.Hq, kvh = h / p.G;
+  const int i0 = qt * 128;
+  const int nk_all = (p.S + 127) / 128;
+  const int nk = CAUSAL ? min(nk_all, min(i0 + 127, p.L - 1) / 128 + 1) : nk_all;
+  bwd_setup<C>(sm, p, warp, lane);
+  const uint32_t tmem = *sm.tmem_base();
+  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+
+  auto pointwise = [&]() {
+    // pointwise pass, one thread per query row
+    const int row = threadIdx.x;
+    const int i = i0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const bool live = i < p.L;
+    const float lse2 = live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
+    const float delta = live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
+    for (int t = 0; t < nk; ++t) {
+      FLB_BWAIT(sm, BB_SP_FULL, t & 1);
+      tc_fence_after();
+      const int j0 = t * 128;
+      const bool partial = CAUSAL && j0 + 127 > i0;
+#pragma unroll
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t s[32], dp[32], pk[16];
+        tmem_ld32_sync(tS + lane_off + c0, s);
+        tmem_ld32_sync(tdP + lane_off + c0, dp);
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float ds[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float pr = ex2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -lse2));
+            float g = pr * (__uint_as_float(dp[c + e]) - delta) * p.scale;
+            if (partial && j0 + c0 + c + e > i) g = 0.f;
+            ds[e] = g;
+          }
+          pk[c >> 1] = pack_bf16(ds[0], ds[1]);
+        }
+        tmem_st16(tS + lane_off + (c0 >> 1), pk);  // dS (bf16) over the columns of S already read
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(sm.bar(BB_DS_FULL));
+    }
+    // epilogue: dQ tile -> bf16 -> shared memory (the Q tile is dead) -> TMA store
+    if (nk > 0) {
+      FLB_BWAIT(sm, BB_ACC_DONE, 0);
+      tc_fence_after();
+      bwd_stage_rows<C>(tdQ + lane_off, sm.res(0), row, 1.0f);
+    } else {
+      // no key tile (cannot happen with L, S > 0): zeros
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(1, 128);
+    if (row == 0 && nk > 0) {
+#pragma unroll
+      for (int b = 0; b < C::NB; ++b)
+        tma_store_4d(&tmdQ, smem_u32(sm.res(0)) + b * C::BOX_BYTES, b * 64, i0, h, n);
+      tma_store_commit();
+      tma_store_wait_read();
+    }
+  };
+  auto issue = [&]() {
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    if (nk > 0) {
+      FLB_BWAIT(sm, BB_RES_FULL, 0);
+      for (int t = 0; t < nk; ++t) {
+        const int slot = t % C::NSLOT;
+        FLB_BWAIT(sm, BB_RING_FULL + slot, (t / C::NSLOT) & 1);
+        tc_fence_after();
+        bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(slot, 0));    // S  = Q K^T
+        bwd_mma_scores<C>(leader, tdP, sm.res(1), sm.slot(slot, 1));   // dP = dO V^T
+        umma_commit_c(leader, sm.bar(BB_SP_FULL));
+        FLB_BWAIT(sm, BB_DS_FULL, t & 1);
+        tc_fence_after();
+        bwd_mma_acc<C>(leader, tdQ, tS, sm.slot(slot, 0), t > 0);      // dQ += dS K
+        umma_commit_c(leader, sm.bar(BB_RING_EMPTY + slot));
+      }
+      umma_commit_c(leader, sm.bar(BB_ACC_DONE));
+    }
+  };
+  auto produce = [&]() {
+    if (nk > 0) {
+      mbar_arrive_expect_tx(sm.bar(BB_RES_FULL), 2 * C::TILE_BYTES);
+      bwd_load_tile<C>(sm.res(0), &tmQ, sm.bar(BB_RES_FULL), i0, h, n);
+      bwd_load_tile<C>(sm.res(1), &tmdO, sm.bar(BB_RES_FULL), i0, h, n);
+      for (int t = 0; t < nk; ++t) {
+        const int slot = t % C::NSLOT;
+        FLB_BWAIT(sm, BB_RING_EMPTY + slot, ((t / C::NSLOT) & 1) ^ 1);
+        mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), 2 * C::TILE_BYTES);
+        bwd_load_tile<C>(sm.slot(slot, 0), &tmK, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
+        bwd_load_tile<C>(sm.slot(slot, 1), &tmV, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
+      }
+    }
+  };
+  if (warp < 4) pointwise();
+  else if (warp == 4) { issue(); __syncwarp(); }
+  else if (warp == 5 && lane == 0) produce();
+  bwd_exit<C>(sm, p, warp);
+}
+
+// ------------------------------------------------------------------------------------------
+// dK, dV
+// ------------------------------------------------------------------------------------------
+template <int D, bool CAUSAL>
+__global__ void __launch_bounds__(256, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
+                    const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
+                    const __grid_constant__ BwdParams p) {
+  using C = BwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem<C> sm{reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023))};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkt = (p.S + 127) / 128, nq = (p.L + 127) / 128;
+  // the first key tiles see the most queries under the causal mask: block order is already heaviest first
+  const int kt = static_cast<int>(blockIdx.x) / (p.N * p.Hkv);
+  const int nh = static_cast<int>(blockIdx.x) % (p.N * p.Hkv);
+  const int n = nh / p.Hkv, kvh = nh % p.Hkv;
+  const int j0 = kt * 128;
+  const int q_lo = CAUSAL ? min(nq, j0 / 128) : 0;   // first query tile with a row i >= j0
+  const int per_head = nq - q_lo;
+  const int steps = per_head * p.G;                  // (query head of the group, query tile) pairs
+  (void)nkt;
+  bwd_setup<C>(sm, p, warp, lane);
+  const uint32_t tmem = *sm.tmem_base();
+  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 256 + D;
+
+  auto pointwise = [&]() {
+    // pointwise pass, one thread per key row; lse2 / delta of the step's 128 queries go through shared memory
+    const int row = threadIdx.x;
+    const int j = j0 + row;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    auto fetch_vec = [&](int step, float& l2, float& dl) {
+      const int g = step / per_head, qt = q_lo + step % per_head;
+      const int h = kvh * p.G + g, i = qt * 128 + row;
+      const bool live = i < p.L;
+      l2 = live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
+      dl = live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
+    };
+    float nl2 = 0.f, ndl = 0.f;
+    if (steps > 0) {
+      fetch_vec(0, nl2, ndl);
+      sm.vec(0, 0)[row] = nl2;
+      sm.vec(0, 1)[row] = ndl;
+    }
+    for (int t = 0; t < steps; ++t) {
+      if (t + 1 < steps) fetch_vec(t + 1, nl2, ndl);   // in flight while this tile is processed
+      FLB_BWAIT(sm, BB_SP_FULL, t & 1);
+      tc_fence_after();
+      named_bar_sync(1, 128);                          // this step's vectors are in place
+      const int i0 = (q_lo + t % per_head) * 128;
+      const bool partial = CAUSAL && j0 + 127 > i0;
+      const float4* l2v = reinterpret_cast<const float4*>(sm.vec(t & 1, 0));
+      const float4* dlv = reinterpret_cast<const float4*>(sm.vec(t & 1, 1));
+#pragma unroll
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t s[32], dp[32], pp[16], pd[16];
+        tmem_ld32_sync(tS + lane_off + c0, s);
+        tmem_ld32_sync(tdP + lane_off + c0, dp);
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float4 l2 = l2v[(c0 + c) >> 2], dl = dlv[(c0 + c) >> 2];
+          const float l2a[4] = {l2.x, l2.y, l2.z, l2.w}, dla[4] = {dl.x, dl.y, dl.z, dl.w};
+          float pr[4], ds[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pe = ex2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -l2a[e]));
+            if (partial && j > i0 + c0 + c + e) pe = 0.f;   // key after the query
+            pr[e] = pe;
+            ds[e] = pe * (__uint_as_float(dp[c + e]) - dla[e]) * p.scale;
+          }
+          pp[c >> 1] = pack_bf16(pr[0], pr[1]);
+          pp[(c >> 1) + 1] = pack_bf16(pr[2], pr[3]);
+          pd[c >> 1] = pack_bf16(ds[0], ds[1]);
+          pd[(c >> 1) + 1] = pack_bf16(ds[2], ds[3]);
+        }
+        tmem_st16(tS + lane_off + (c0 >> 1), pp);    // P^T (bf16) over the columns of S^T already read
+        tmem_st16(tdP + lane_off + (c0 >> 1), pd);   // dS^T over the columns of dP^T already read
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(sm.bar(BB_DS_FULL));
+      if (t + 1 < steps) {   // the other buffer was last read in step t - 1, before this step's barrier
+        sm.vec((t + 1) & 1, 0)[row] = nl2;
+        sm.vec((t + 1) & 1, 1)[row] = ndl;
+      }
+    }
+    // epilogue: dV and dK tiles -> bf16 -> shared memory (the K and V tiles are dead) -> TMA stores
+    if (steps > 0) {
+      FLB_BWAIT(sm, BB_ACC_DONE, 0);
+      tc_fence_after();
+      bwd_stage_rows<C>(tdV + lane_off, sm.res(1), row, 1.0f);
+      bwd_stage_rows<C>(tdK + lane_off, sm.res(0), row, 1.0f);
+    } else {
+      // a key tile no query sees (causal with S > L): zeros
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < C::TILE_BYTES / 128 / 16; ++c) {
+        reinterpret_cast<uint4*>(sm.res(0) + row * (C::TILE_BYTES / 128))[c] = z;
+        reinterpret_cast<uint4*>(sm.res(1) + row * (C::TILE_BYTES / 128))[c] = z;
+      }
+    }
+    fence_proxy_async_smem();
+    named_bar_sync(2, 128);
+    if (row == 0) {
+#pragma unroll
+      for (int b = 0; b < C::NB; ++b) {
+        tma_store_4d(&tmdK, smem_u32(sm.res(0)) + b * C::BOX_BYTES, b * 64, j0, kvh, n);
+        tma_store_4d(&tmdV, smem_u32(sm.res(1)) + b * C::BOX_BYTES, b * 64, j0, kvh, n);
+      }
+      tma_store_commit();
+      tma_store_wait_read();
+    }
+  };
+  auto issue = [&]() {
+    const uint32_t leader = elect_one() ? 1u : 0u;
+    if (steps > 0) {
+      FLB_BWAIT(sm, BB_RES_FULL, 0);
+      for (int t = 0; t < steps; ++t) {
+        const int slot = t % C::NSLOT;
+        FLB_BWAIT(sm, BB_RING_FULL + slot, (t / C::NSLOT) & 1);
+        tc_fence_after();
+        bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(slot, 0));    // S^T  = K Q^T
+        bwd_mma_scores<C>(leader, tdP, sm.res(1), sm.slot(slot, 1));   // dP^T = V dO^T
+        umma_commit_c(leader, sm.bar(BB_SP_FULL));
+        FLB_BWAIT(sm, BB_DS_FULL, t & 1);
+        tc_fence_after();
+        bwd_mma_acc<C>(leader, tdV, tS, sm.slot(slot, 1), t > 0);      // dV += P^T dO
+        bwd_mma_acc<C>(leader, tdK, tdP, sm.slot(slot, 0), t > 0);     // dK += dS^T Q
+        umma_commit_c(leader, sm.bar(BB_RING_EMPTY + slot));
+      }
+      umma_commit_c(leader, sm.bar(BB_ACC_DONE));
+    }
+  };
+  auto produce = [&]() {
+    if (steps > 0) {
+      mbar_arrive_expect_tx(sm.bar(BB_RES_FULL), 2 * C::TILE_BYTES);
+      bwd_load_tile<C>(sm.res(0), &tmK, sm.bar(BB_RES_FULL), j0, kvh, n);
+      bwd_load_tile<C>(sm.res(1), &tmV, sm.bar(BB_RES_FULL), j0, kvh, n);
+      for (int t = 0; t < steps; ++t) {
+        const int slot = t % C::NSLOT;
+        const int h = kvh * p.G + t / per_head, i0 = (q_lo + t % per_head) * 128;
+        FLB_BWAIT(sm, BB_RING_EMPTY + slot, ((t / C::NSLOT) & 1) ^ 1);
+        mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), 2 * C::TILE_BYTES);
+        bwd_load_tile<C>(sm.slot(slot, 0), &tmQ, sm.bar(BB_RING_FULL + slot), i0, h, n);
+        bwd_load_tile<C>(sm.slot(slot, 1), &tmdO, sm.bar(BB_RING_FULL + slot), i0, h, n);
+      }
+    }
+  };
+  if (warp < 4) pointwise();
+  else if (warp == 4) { issue(); __syncwarp(); }
+  else if (warp == 5 && lane == 0) produce();
+  bwd_exit<C>(sm, p, warp);
+}
+
+}  // namespace flb

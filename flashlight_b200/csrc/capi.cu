@@ -14,10 +14,17 @@
 #include "tmap.h"
 
 namespace {
+std::atomic<uint64_t> g_launches{0};
+}
+
+namespace flb {
+void count_launches(int n) { g_launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+}  // namespace flb
+
+namespace {
 
 using namespace flb;
 
-std::atomic<uint64_t> g_launches{0};
 
 // Scratch for flb200_attn_fwd_noalloc: lives in the library image of every device that loads it.
 // In host code `g_noalloc_scratch` is only a stand-in for the symbol; the device address comes
@@ -286,8 +293,10 @@ ResidentPlan plan_resident(const flb200_attn_params* p, int width) {
 }
 
 int check_arch() {
+  // cudaSetDevice binds the device's primary context to the calling thread: the tensor-map encoder is a
+  // driver call and needs one even in a thread that has made no runtime call yet
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return FLB200_E_LAUNCH;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return FLB200_E_LAUNCH;
   int major = 0;
   if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
     return FLB200_E_LAUNCH;

@@ -260,6 +260,72 @@ def _attn_fwd_fake(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap,
     return q.new_empty((N, Ho, L, Ev))
 
 
+def attn_bwd(q, k, v, o, dout, lse, scale: float, causal: bool):
+    """dq, dk, dv of plain / causal attention (GQA by head counts) from the forward's inputs, output and
+    log-sum-exp and the output's gradient: q, o, dout [N, Hq, L, E]; k, v [N, Hkv, S, E]; lse fp32
+    [N, Hq, L] as `attn_fwd_lse` returns it.  The reference stubs its backward
+    (benchmarks/_utils.py:16-21); this is the derivative of its eager functions."""
+    lib = _lib.load()
+    for t in (q, k, v, o, dout):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 4:
+            raise ValueError("flb200: attn_bwd takes 4-D bfloat16 CUDA tensors")
+    N, Hq, L, E = q.shape
+    Hkv, S = k.size(1), k.size(2)
+    if v.shape != k.shape or o.shape != q.shape or dout.shape != q.shape:
+        raise ValueError("flb200: attn_bwd needs equal q/k and v head dims and matching shapes")
+    dout = dout if dout.stride(3) == 1 else dout.contiguous()
+    o = o if o.stride(3) == 1 else o.contiguous()
+    lse = lse.contiguous()
+    dq, dk, dv = torch.empty_like(q, memory_format=torch.contiguous_format), \
+        torch.empty_like(k, memory_format=torch.contiguous_format), torch.empty_like(v, memory_format=torch.contiguous_format)
+    p = _lib.AttnBwdParams()
+    p.struct_size = C.sizeof(_lib.AttnBwdParams)
+    p.N, p.Hq, p.Hkv, p.L, p.S, p.E = N, Hq, Hkv, L, S, E
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("dout", dout), ("dq", dq), ("dk", dk), ("dv", dv)):
+        setattr(p, name, t.data_ptr())
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", o), ("do_stride", dout),
+                    ("dq_stride", dq), ("dk_stride", dk), ("dv_stride", dv)):
+        arr = getattr(p, name)
+        arr[0], arr[1], arr[2] = _strides3(t)
+    p.lse = lse.data_ptr()
+    p.lse_stride[0], p.lse_stride[1] = lse.stride(0), lse.stride(1)
+    p.scale, p.causal = float(scale), int(causal)
+    ws = torch.empty(max(lib.flb200_attn_bwd_workspace_bytes(C.byref(p)), 256), dtype=torch.uint8, device=q.device)
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    p.status = _status_word(q.device).data_ptr()
+    mirror = _status_mirror(q.device)
+    if int(mirror[0]) != 0:
+        check_status(q.device)
+    p.status_host = mirror.data_ptr()
+    with torch.cuda.device(q.device):
+        rc = lib.flb200_attn_bwd(C.byref(p), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+    if rc != _lib.OK:
+        _raise_for(rc, "attn_bwd")
+    return dq, dk, dv
+
+
+class _AttentionWithGrad(torch.autograd.Function):
+    """Plain / causal attention whose backward runs the library's backward kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal):
+        o, lse = attn_fwd_lse(q, k, v, scale, mask=_lib.MASK_CAUSAL if causal else _lib.MASK_NONE)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.scale, ctx.causal = scale, causal
+        return o
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = attn_bwd(q, k, v, o, dout.to(torch.bfloat16), lse, ctx.scale, ctx.causal)
+        return dq, dk, dv, None, None
+
+
+def attention_with_grad(q, k, v, scale: float, causal: bool) -> torch.Tensor:
+    """softmax(q k^T * scale [causal]) v, differentiable with respect to q, k and v."""
+    return _AttentionWithGrad.apply(q, k, v, float(scale), bool(causal))
+
+
 _POINTWISE = {"identity": _lib.PW_IDENTITY, "relu": _lib.PW_RELU, "tanh": _lib.PW_TANH, "sigmoid": _lib.PW_SIGMOID}
 
 

@@ -237,6 +237,47 @@ int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream);
  */
 int flb200_selftest_wait_timeout(const flb200_attn_params* p, void* cuda_stream);
 
+/*
+ * Backward pass of plain and causal attention (with grouped query heads): dq, dk, dv from the
+ * forward's inputs, its output `o`, its log-sum-exp `lse` (flb200_attn_params.lse of the forward call)
+ * and the output's gradient `dout`.  The reference stubs its backward (benchmarks/_utils.py:16-21), so
+ * there is no reference kernel to cite; the arithmetic is the derivative of
+ * attention_variants/vanilla.py:4-35 and causal.py:4-36:
+ *   P = exp(q k^T * scale - lse), dV = P^T dO, dP = dO V^T, dS = P (dP - rowsum(dO o)) * scale,
+ *   dQ = dS K, dK = dS^T Q   (sums over the query heads of a group for dK, dV).
+ * All tensors bf16 with the layouts and stride conventions of the forward's parameter block: q, o,
+ * dout, dq are [N][Hq][L][E]; k, v, dk, dv are [N][Hkv][S][E]; head dims up to 128, the same for q/k
+ * and v.
+ * `workspace`: flb200_attn_bwd_workspace_bytes() bytes of device scratch (fp32 row sums), 256-byte
+ * aligned.  Three launches on `cuda_stream`.
+ */
+typedef struct flb200_attn_bwd_params {
+  uint32_t struct_size;
+  int32_t N, Hq, Hkv, L, S, E;
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* o;
+  const void* dout;
+  const float* lse;       /* [N][Hq][L] natural log, element strides {batch, head} */
+  void* dq;
+  void* dk;
+  void* dv;
+  int64_t q_stride[3], k_stride[3], v_stride[3], o_stride[3], do_stride[3];
+  int64_t dq_stride[3], dk_stride[3], dv_stride[3];
+  int64_t lse_stride[2];
+  float scale;
+  int32_t causal;         /* 0: no mask, 1: keep j <= i */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;        /* as in flb200_attn_params */
+  int32_t* status_host;
+  uint32_t wait_limit_us;
+} flb200_attn_bwd_params;
+
+size_t flb200_attn_bwd_workspace_bytes(const flb200_attn_bwd_params* p);
+int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream);
+
 /* Map the value read back from a status word to a flb200_status
  * (0 -> FLB200_OK, timeout code -> FLB200_E_TIMEOUT).  If `barrier` / `block`
  * are non-NULL they receive which wait expired and the low 16 bits of the index of the thread

@@ -1,0 +1,91 @@
+"""Backward kernels (dq, dk, dv of plain and causal attention, with grouped query heads) against torch
+autograd through the fp32 oracle on the same bf16-rounded inputs.  The reference stubs its backward
+(benchmarks/_utils.py:16-21), so the oracle's derivative is the definition.
+
+Tolerance: gradients have no fixed scale (they grow with the upstream gradient and shrink with the
+sequence length), so the band is relative to each gradient's own RMS: |d - ref| <= 2e-2 * rms(ref) +
+1.6e-2 * |ref| elementwise (the bf16 rounding of P, dS and the result), mean |d - ref| <= 4e-3 * rms(ref)
+(measured: 1.5e-3).  Under the causal mask the first few query rows see one to five keys: their
+probabilities are of order one, the terms of their gradients cancel, and the bf16 rounding of those
+terms shows in a few elements per hundred thousand (measured at most 62 per million, the largest at 1.5
+times the band); the test allows 2 per ten thousand outside the band and none beyond three times it.
+"""
+import pytest
+import torch
+
+import flashlight_b200
+from flashlight_b200 import attention_variants as av
+from oracle import attention_oracle as ao
+
+pytestmark = pytest.mark.gpu
+
+
+def rnd(shape, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g).to(torch.bfloat16).cuda()
+
+
+def grads(fn, q, k, v, dout):
+    q, k, v = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+    out = fn(q, k, v)
+    out.backward(dout.reshape(out.shape).to(out.dtype))
+    return out.detach(), q.grad, k.grad, v.grad
+
+
+def close(d, ref, what):
+    flashlight_b200.check_status()
+    d, ref = d.float(), ref.float()
+    rms = ref.pow(2).mean().sqrt().item()
+    err = (d - ref).abs()
+    band = 2e-2 * rms + 1.6e-2 * ref.abs()
+    assert torch.isfinite(d).all(), what
+    outside = int((err > band).sum())
+    assert outside <= max(1, 2 * err.numel() // 10_000), (what, outside, err.numel())
+    assert bool((err <= 3 * band).all()), (what, (err / band).max().item(), rms)
+    assert err.mean().item() <= 4e-3 * rms, (what, err.mean().item(), rms)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("S", [128, 384, 1000])
+def test_backward_matches_autograd_of_the_oracle(S, D, causal):
+    N, Hq, Hkv = 2, 4, 2
+    q, k, v = rnd((N, Hq, S, D), 1), rnd((N, Hkv, S, D), 2), rnd((N, Hkv, S, D), 3)
+    dout = rnd((N, Hq, S, D), 4)
+    if causal:
+        fn = lambda a, b, c: av.attention_pytorch_causal(a, b, c, enable_gqa=True)
+        fo = lambda a, b, c: ao.causal(a, b, c, enable_gqa=True)
+    else:
+        fn = lambda a, b, c: av.attention_pytorch(a, b, c, enable_gqa=True)
+        fo = lambda a, b, c: ao.vanilla(a, b, c, enable_gqa=True)
+    out, dq, dk, dv = grads(fn, q, k, v, dout)
+    ref, rq, rk, rv = grads(fo, q.float(), k.float(), v.float(), dout.float())
+    assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == v.shape
+    close(dv, rv, ("dv", S, D, causal))
+    close(dq, rq, ("dq", S, D, causal))
+    close(dk, rk, ("dk", S, D, causal))
+
+
+def test_backward_cross_lengths_and_narrow_heads():
+    q, k, v = rnd((1, 2, 200, 48), 5), rnd((1, 2, 520, 48), 6), rnd((1, 2, 520, 48), 7)
+    dout = rnd((1, 2, 200, 48), 8)
+    _, dq, dk, dv = grads(lambda a, b, c: av.attention_pytorch(a, b, c), q, k, v, dout)
+    _, rq, rk, rv = grads(lambda a, b, c: ao.vanilla(a, b, c), q.float(), k.float(), v.float(), dout.float())
+    close(dq, rq, "dq")
+    close(dk, rk, "dk")
+    close(dv, rv, "dv")
+
+
+def test_variants_without_a_backward_kernel_say_so():
+    q = rnd((1, 2, 128, 64), 9).requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        av.attention_pytorch_sliding_window(q, q, q, window_size=16)
+
+
+def test_backward_is_deterministic():
+    q, k, v, dout = rnd((1, 4, 700, 128), 10), rnd((1, 1, 700, 128), 11), rnd((1, 1, 700, 128), 12), rnd((1, 4, 700, 128), 13)
+    fn = lambda a, b, c: av.attention_pytorch_causal(a, b, c, enable_gqa=True)
+    first = grads(fn, q, k, v, dout)
+    for _ in range(3):
+        again = grads(fn, q, k, v, dout)
+        assert all(torch.equal(x, y) for x, y in zip(first, again))
