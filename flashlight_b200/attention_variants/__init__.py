@@ -9,6 +9,7 @@ from .document_mask import attention_pytorch_document_mask, create_document_id
 from .prefix_lm import attention_pytorch_prefix_lm, get_prefix_lm_mask
 from .diff_attn import diffattn
 from .evoformer import attention_reference
+from .ipa import invariant_point_attention
 
 __all__ = [
     "attention_pytorch", "attention_pytorch_nogqa", "attention_pytorch_causal",
@@ -17,5 +18,5 @@ __all__ = [
     "attention_pytorch_sliding_window", "get_sliding_mask",
     "attention_pytorch_document_mask", "create_document_id",
     "attention_pytorch_prefix_lm", "get_prefix_lm_mask",
-    "diffattn", "attention_reference",
+    "diffattn", "attention_reference", "invariant_point_attention",
 ]

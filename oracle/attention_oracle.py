@@ -260,3 +260,28 @@ def product_chain(a, b, c, pointwise: str = "identity", scale: float = 1.0, dtyp
     mid = f(torch.matmul(a.to(dtype), b.to(dtype)) * scale)
     mid = mid.to(torch.bfloat16).to(dtype)
     return torch.matmul(mid, c.to(dtype))
+
+
+def invariant_point_attention(q_scalar, k_scalar, v_scalar, q_points, k_points, v_points, pair_bias,
+                              c_hidden: int = 64, no_qk_points: int = 8, dtype=torch.float32):
+    """Invariant point attention as the reference's fusion test states it (tests/test_ipa.py:57-125).
+
+    Scalars are [B, H, N, C], points [B, H, N, P, 4], the pair bias [B, H, N, N].  The logits are
+    q.k / sqrt(c_hidden) + w * sum_p |q_p - k_p|^2 + bias with w = -0.5 sqrt(9 / (2 no_qk_points))
+    (test_ipa.py:83-108); the frame transforms and the residue mask are commented out there
+    (test_ipa.py:86-88,110-111,124) and are therefore not applied here either.  Returns the two
+    aggregates of test_ipa.py:118-124: the scalar output [B, H, N, C] and the point output in the
+    einsum's order [B, N, H, P_v, 4].  The reference's last line adds the two, which broadcasts only
+    for contrived shapes (C == 4, B == 1, N == P_v); the golden fixture uses such a shape with one of
+    the two value operands zeroed to read each aggregate out of the unmodified function.
+    """
+    q, k, v = (t.to(dtype) for t in (q_scalar, k_scalar, v_scalar))
+    qp, kp, vp = (t.to(dtype) for t in (q_points, k_points, v_points))
+    content = (q / (c_hidden ** 0.5)) @ k.transpose(-1, -2)
+    dist_sq = ((qp.unsqueeze(3) - kp.unsqueeze(2)) ** 2).sum(dim=-1)  # [B, H, N, N, P]
+    w = -0.5 * (9.0 / (2 * no_qk_points)) ** 0.5
+    logits = content + dist_sq.sum(dim=-1) * w + pair_bias.to(dtype)
+    a = torch.softmax(logits, dim=-1)
+    out_scalar = a @ v
+    out_points = torch.einsum("...hij,...hjpv->...ihpv", a, vp)
+    return out_scalar, out_points

@@ -99,6 +99,27 @@ def main(ref_root: str) -> None:
     v = rnd(g, 1, 2, 200, 256)
     cases["diff_d128"] = dict(q=q, k=k, v=v, lam=0.2, out=diff_attn.diffattn(*f32(q, k, v)))
 
+    # invariant point attention: the function lives in the reference's test file (tests/test_ipa.py:57-125)
+    # and ends by adding the scalar output [B, H, N, C] to the point output [B, N, H, P_v, 4], which
+    # broadcasts only when C == 4, B == 1 and N == P_v.  At such a shape the unmodified function is run
+    # twice, once per zeroed value operand, and each aggregate is read out of the sum.
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_test_ipa", str(Path(ref_root) / "tests" / "test_ipa.py"))
+    ipa_mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ipa_mod)
+    H, N, C, Pqk = 3, 24, 4, 4
+    qs, ks, vs = rnd(g, 1, H, N, C), rnd(g, 1, H, N, C), rnd(g, 1, H, N, C)
+    qp, kp, vp = rnd(g, 1, H, N, Pqk, 4), rnd(g, 1, H, N, Pqk, 4), rnd(g, 1, H, N, N, 4)
+    pb = rnd(g, 1, H, N, N)
+    # the function builds a per-head view of the frames and never uses it (test_ipa.py:77-88)
+    frames = ipa_mod.Rigid(torch.nn.functional.normalize(rnd(g, 1, N, 4).float(), dim=-1), rnd(g, 1, N, 3).float())
+    ipa = lambda v_s, v_p: ipa_mod.invariant_point_attention(
+        *f32(qs, ks, v_s, qp, kp, v_p, pb), frames, torch.ones(1, N), c_hidden=C, no_qk_points=Pqk)
+    points = ipa(torch.zeros_like(vs), vp)           # [1, N, H, P_v, 4]
+    scalar = ipa(vs, torch.zeros_like(vp))[0, 0]     # [H, N(=P_v), C(=4)], the same for every query row
+    cases["ipa"] = dict(q=qs, k=ks, v=vs, q_points=qp, k_points=kp, v_points=vp, pair_bias=pb, c_hidden=C,
+                        no_qk_points=Pqk, out=scalar.unsqueeze(0), out_points=points)
+
     for name, c in cases.items():
         c["out"] = c["out"].contiguous()
         torch.save(c, HERE / f"{name}.pt")

@@ -83,6 +83,16 @@ def test_evoformer(name):
     close(ao.evoformer(c["q"], c["k"], c["v"], [c["bias1"], c["bias2"]]), c["out"])
 
 
+def test_invariant_point_attention():
+    """Both aggregates, read out of the unmodified reference function at a shape where its final sum
+    broadcasts (tests/golden/make_golden.py says how)."""
+    c = load("ipa")
+    scalar, points = ao.invariant_point_attention(c["q"], c["k"], c["v"], c["q_points"], c["k_points"], c["v_points"],
+                                                  c["pair_bias"], c_hidden=c["c_hidden"], no_qk_points=c["no_qk_points"])
+    close(scalar, c["out"])
+    close(points, c["out_points"])
+
+
 def test_extensions_reduce_to_reference_when_off():
     """Extension flags default to the reference's behaviour; causal composition equals the
     causal oracle when the score modifier is the identity (cap -> infinity)."""
