@@ -310,6 +310,55 @@ def time_per_launch(w, copies, steps, run_product, inside=None):
     return [a.elapsed_time(b) for a, b in evs]
 
 
+def adjacent_rows(steps, peak_tf):
+    """The operators either side of the forward variants, one line each: the backward pass at the default
+    workload's shape (algorithmic FLOPs = 2.5 x the forward's: five matrix products for two), the product
+    chain `(A @ B) @ C` at the reference's test shape (monkeypatch/template/fused_bmm.py:437-449) and
+    invariant point attention at a structure module's sizes."""
+    from flashlight_b200 import _lib, ops
+    from flashlight_b200 import attention_variants as av
+    from flashlight_b200.monkeypatch.template.fused_bmm import fused_bmm
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(int(2.0e6))
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    r = lambda *shape: torch.randn(*shape, device="cuda", dtype=torch.bfloat16)
+    rows = {}
+    N, Hq, Hkv, S, D = 8, 32, 8, 4096, 128
+    q, k, v, dout = r(N, Hq, S, D), r(N, Hkv, S, D), r(N, Hkv, S, D), r(N, Hq, S, D)
+    o, lse = ops.attn_fwd_lse(q, k, v, D ** -0.5, mask=_lib.MASK_CAUSAL)
+    ms = timed(lambda: ops.attn_bwd(q, k, v, o, dout, lse, D ** -0.5, True))
+    fl = 2.5 * 4 * D * N * Hq * (S * (S + 1) // 2)
+    rows["backward_causal_gqa"] = {"shape": "B8 Hq32 Hkv8 S4096 D128 causal", "ms": ms, "flops": fl,
+                                   "tflops": fl / ms / 1e9, "tensor_frac": fl / ms / 1e9 / peak_tf, "launches_per_step": 3}
+    del q, k, v, dout, o, lse
+    a, b, c = r(16, 4096, 128), r(16, 128, 4096), r(16, 4096, 128)
+    ms = timed(lambda: fused_bmm(a, b, c))
+    fl = 4.0 * 16 * 4096 * 4096 * 128
+    rows["product_chain"] = {"shape": "b16 [4096,128]@[128,4096]@[4096,128]", "ms": ms, "flops": fl,
+                             "tflops": fl / ms / 1e9, "tensor_frac": fl / ms / 1e9 / peak_tf, "launches_per_step": 1}
+    del a, b, c
+    B, H, Nr, C, Pq, Pv = 8, 12, 384, 16, 4, 8
+    args = (r(B, H, Nr, C), r(B, H, Nr, C), r(B, H, Nr, C), r(B, H, Nr, Pq, 4), r(B, H, Nr, Pq, 4), r(B, H, Nr, Pv, 4),
+            r(B, H, Nr, Nr))
+    ms = timed(lambda: av.invariant_point_attention(*args, None, None, c_hidden=C, no_qk_points=Pq))
+    fl = 2.0 * B * H * Nr * Nr * ((C + 4 * Pq) + (C + 4 * Pv))
+    rows["invariant_point_attention"] = {"shape": "B8 H12 N384 C16 P_qk4 P_v8", "ms": ms, "flops": fl,
+                                         "tflops": fl / ms / 1e9, "note": "operand assembly by torch ops inside the time",
+                                         "launches_per_step": 1}
+    return rows
+
+
 def roof(flops, hbm_bytes, ms, peak_tf, peak_hbm):
     """The roof that bounds a launch, min(tensor, HBM), and the fraction of it that was reached."""
     t_tensor = flops / (peak_tf * 1e12)
@@ -483,6 +532,11 @@ def main():
             table[name] = row
             del cps
 
+    adjacent = None
+    if rank == 0 and world == 1 and not args.no_workloads:
+        adjacent = adjacent_rows(max(3, min(args.steps, 10)), peak_tf)
+        flashlight_b200.check_status()
+
     # ---- CPU baseline on a bounded sample ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -524,6 +578,8 @@ def main():
         }
         if table is not None:
             line["workloads"] = table
+        if adjacent is not None:
+            line["adjacent_rows"] = adjacent
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
