@@ -58,10 +58,10 @@ cudaError_t launch_bwd(const flb200_attn_bwd_params* p, const BwdParams& bp, con
   e = cudaFuncSetAttribute(dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   const int nq = (p->L + 127) / 128, nk = (p->S + 127) / 128;
-  dkv<<<nk * p->N * p->Hkv, 256, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdK, tmdV, bp);
+  dkv<<<nk * p->N * p->Hkv, kBwdThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdK, tmdV, bp);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dq<<<nq * p->N * p->Hq, 256, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, bp);
+  dq<<<nq * p->N * p->Hq, kBwdThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, bp);
   return cudaGetLastError();
 }
 
@@ -121,7 +121,7 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
     return FLB200_E_LAUNCH;
 
   const int rows = p->N * p->Hq * bp.Lp;
-  attn_bwd_delta_kernel<<<rows / 8, 256, 0, stream>>>(
+  attn_bwd_delta_kernel<<<rows / 16, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->dout), p->o_stride[0],
       p->o_stride[1], p->o_stride[2], p->do_stride[0], p->do_stride[1], p->do_stride[2], p->E, p->Hq, p->L, bp.Lp,
       bp.delta);

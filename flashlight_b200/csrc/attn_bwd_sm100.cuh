@@ -3,7 +3,7 @@
 //
 // Three kernels, none of which needs an atomic or a transpose in memory:
 //
-//   attn_bwd_delta_kernel   delta[i] = sum_d dO[i][d] * O[i][d]  (fp32, one warp per query row)
+//   attn_bwd_delta_kernel   delta[i] = sum_d dO[i][d] * O[i][d]  (fp32, sixteen lanes per query row)
 //
 //   attn_bwd_dq_kernel      one CTA per (batch, query head, 128-row query tile); walks the key tiles:
 //                             S = Q K^T, dP = dO V^T            (tcgen05 SS products into tensor memory)
@@ -18,9 +18,14 @@
 //
 // The score products are recomputed in both kernels (7 tile products per pair of tiles instead of 5);
 // in exchange every accumulator stays in one CTA's tensor memory from start to finish.
-// Tensor memory: S 128 + dP 128 + accumulators (D for dQ; 2 D for dV, dK) <= 512 columns, one CTA per
-// SM.  256 threads: warps 0-3 pointwise pass and epilogue (one thread per tensor-memory lane), warp 4
-// MMA issue, warp 5 TMA producer.  All waits are bounded as in the forward kernel.
+// Tensor memory, one CTA per SM: dQ kernel S 128 + dP 2 x 128 (two buffers) + dQ D; dK/dV kernel
+// S 128 + dP 128 + dV D + dK D (all 512 columns at D = 128).  320 threads: warps 0-7 pointwise pass and
+// epilogue (two threads per tensor-memory lane, 64 of the tile's 128 columns each), warp 8 MMA issue,
+// warp 9 TMA producer.  In the dQ kernel the products of the next key tile run under the pointwise
+// pass of the current one: a thread first turns its 64 scores into probabilities held in registers and
+// hands the score columns back, so S(t+1) and dP(t+1) (into the other dP buffer) are issued while
+// dS(t) = P (dP - delta) scale is formed and written over the dP(t) columns for the dQ product.
+// All waits are bounded as in the forward kernel.
 #pragma once
 #include <cuda.h>
 #include <math_constants.h>
@@ -44,13 +49,20 @@ struct BwdParams {
 
 enum : int {
   BB_RES_FULL = 0,  // the CTA's resident tiles (Q, dO or K, V) have landed
-  BB_SP_FULL = 1,   // MMA -> pointwise: both score tiles written
-  BB_DS_FULL = 2,   // pointwise -> MMA: P / dS written back (128 arrivals)
-  BB_ACC_DONE = 3,  // MMA -> epilogue: accumulators final
-  BB_RING_FULL = 4,   // +slot
-  BB_RING_EMPTY = 8,  // +slot
-  BB_COUNT = 12
+  BB_SP_FULL = 1,   // MMA -> pointwise: score tile written (dK/dV kernel: both tiles)
+  BB_S_FREE = 2,    // pointwise -> MMA: the score columns have been read (dQ kernel, 256 arrivals)
+  BB_DP_FULL = 6,   // +buffer, MMA -> pointwise: dP written (dQ kernel)
+  BB_DS_FULL = 4,   // pointwise -> MMA: P / dS written back (256 arrivals)
+  BB_ACC_DONE = 5,  // MMA -> epilogue: accumulators final
+  BB_RING_FULL = 8,    // +slot: the slot's first tile (dQ kernel: K), or both (dK/dV kernel)
+  BB_RING_EMPTY = 12,  // +slot
+  BB_RING2_FULL = 16,  // +slot: the slot's second tile (dQ kernel: V)
+  BB_RING2_EMPTY = 20, // +slot
+  BB_COUNT = 24
 };
+static_assert(BB_COUNT * 8 <= 256, "the barriers end where the tensor-memory base word begins");
+constexpr int kBwdPointwiseThreads = 256;
+constexpr int kBwdThreads = kBwdPointwiseThreads + 64;
 
 template <int D_>
 struct BwdCfg {
@@ -77,8 +89,8 @@ struct BwdSmem {
   }
   FLB_DEV uint8_t* aux() const { return base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES + C::VEC_BYTES; }
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
-  FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 128); }
-  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 132); }
+  FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }  // after BB_COUNT barriers
+  FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
 };
 
 #define FLB_BWAIT(sm, id, parity)                                 \
@@ -119,7 +131,9 @@ FLB_DEV void bwd_mma_scores(uint32_t leader, uint32_t d_tmem, const void* a_tile
   }
 }
 
-// D[tmem 128 x D] (+)= A[tmem 128 x 128, bf16] * B[128 x D], B an MN-major tile in shared memory
+// D[tmem 128 x D] (+)= A[tmem 128 x 128, bf16] * B[128 x D], B an MN-major tile in shared memory.  The A
+// operand lies where the two pointwise threads of a lane wrote it: contraction indices 0-63 in columns
+// 0-31 of the score buffer, 64-127 in columns 64-95 (each thread writes over columns it has read itself).
 template <class C>
 FLB_DEV void bwd_mma_acc(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, const void* b_tile, bool accumulate) {
   using Ds = BwdDesc<C>;
@@ -129,7 +143,7 @@ FLB_DEV void bwd_mma_acc(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, cons
   else umma_ts_c<0>(leader, d_tmem, a_tmem, b, Ds::mn_hi, idesc);
 #pragma unroll
   for (int k = 1; k < 8; ++k)
-    umma_ts_c<1>(leader, d_tmem, a_tmem + k * 8, b + ((k * 16 * 128) >> 4), Ds::mn_hi, idesc);
+    umma_ts_c<1>(leader, d_tmem, a_tmem + (k / 4) * 64 + (k % 4) * 8, b + ((k * 16 * 128) >> 4), Ds::mn_hi, idesc);
 }
 
 template <class C>
@@ -141,11 +155,12 @@ FLB_DEV void bwd_load_tile(uint8_t* dst, const CUtensorMap* tm, uint32_t bar, in
 
 // accumulator rows (fp32, `D` columns at `t_acc`) -> bf16 tile in shared memory in the layout of the
 // output tensor map (128-byte swizzled boxes of 64 columns)
-template <class C>
-FLB_DEV void bwd_stage_rows(uint32_t t_acc, uint8_t* tile, int row, float mul) {
+template <class C, int COLS>
+FLB_DEV void bwd_stage_rows(uint32_t t_acc, uint8_t* tile, int row, int col_first, float mul) {
   const int sw = row & 7;
 #pragma unroll
-  for (int c0 = 0; c0 < C::D; c0 += 32) {
+  for (int cc = 0; cc < COLS; cc += 32) {
+    const int c0 = col_first + cc;
     uint32_t o[32];
     tmem_ld32_sync(t_acc + c0, o);
 #pragma unroll
@@ -169,7 +184,7 @@ FLB_DEV void bwd_setup(const BwdSmem<C>& sm, const BwdParams& p, int warp, int l
       sm.ctl()->fail_bar = -1;
       sm.ctl()->limit_us = p.wait_limit_us;
     }
-    if (lane < BB_COUNT) mbar_init(sm.bar(lane), lane == BB_DS_FULL ? 128 : 1);
+    if (lane < BB_COUNT) mbar_init(sm.bar(lane), lane == BB_DS_FULL || lane == BB_S_FREE ? kBwdPointwiseThreads : 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -179,7 +194,7 @@ FLB_DEV void bwd_setup(const BwdSmem<C>& sm, const BwdParams& p, int warp, int l
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (threadIdx.x == 7 * 32 && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0)
+  if (threadIdx.x == 9 * 32 + 1 && p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0)
     sm.ctl()->abort = 1;
 }
 
@@ -207,25 +222,39 @@ FLB_DEV void bwd_exit(const BwdSmem<C>& sm, const BwdParams& p, int warp) {
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       int64_t o_sn, int64_t o_sh, int64_t o_sl, int64_t do_sn, int64_t do_sh,
                                       int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta) {
-  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);  // one warp per (n, h, i)
-  const int lane = threadIdx.x & 31;
+  // 16 lanes per (n, h, i) row, 8 features (one 16-byte load per tensor) per lane; rows start on 16-byte
+  // boundaries (pointers and strides are checked by the host)
+  const int row = blockIdx.x * 16 + (threadIdx.x >> 4);
+  const int sub = threadIdx.x & 15;
   const int i = row % Lp, nh = row / Lp, h = nh % Hq, n = nh / Hq;
   float acc = 0.f;
-  if (i < L) {
-    const __nv_bfloat16* po = o + n * o_sn + h * o_sh + i * o_sl;
-    const __nv_bfloat16* pd = d_o + n * do_sn + h * do_sh + i * do_sl;
-    for (int d = lane; d < E; d += 32) acc = fmaf(__bfloat162float(po[d]), __bfloat162float(pd[d]), acc);
+  const int d = sub * 8;
+  if (i < L && d < E) {
+    const __nv_bfloat16* po = o + n * o_sn + h * o_sh + i * o_sl + d;
+    const __nv_bfloat16* pd = d_o + n * do_sn + h * do_sh + i * do_sl + d;
+    if (d + 8 <= E) {
+      const uint4 a = *reinterpret_cast<const uint4*>(po), b = *reinterpret_cast<const uint4*>(pd);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        // a bf16 is the upper half of an fp32
+        acc = fmaf(__uint_as_float(aw[w] << 16), __uint_as_float(bw[w] << 16), acc);
+        acc = fmaf(__uint_as_float(aw[w] & 0xffff0000u), __uint_as_float(bw[w] & 0xffff0000u), acc);
+      }
+    } else {
+      for (int e = 0; d + e < E; ++e) acc = fmaf(__bfloat162float(po[e]), __bfloat162float(pd[e]), acc);
+    }
   }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) delta[row] = acc;
+  for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (sub == 0) delta[row] = acc;
 }
 
 // ------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------
 template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmdQ, const __grid_constant__ BwdParams p) {
@@ -243,39 +272,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int nk = CAUSAL ? min(nk_all, min(i0 + 127, p.L - 1) / 128 + 1) : nk_all;
   bwd_setup<C>(sm, p, warp, lane);
   const uint32_t tmem = *sm.tmem_base();
-  const uint32_t tS = tmem, tdP = tmem + 128, tdQ = tmem + 256;
+  const uint32_t tS = tmem, tdP0 = tmem + 128, tdQ = tmem + 384;   // dP buffer b at tdP0 + 128 b
 
   auto pointwise = [&]() {
-    // pointwise pass, one thread per query row
-    const int row = threadIdx.x;
+    // pointwise pass: thread (row, half) owns columns [64 half, 64 half + 64) of the row's scores
+    const int row = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int i = i0 + row;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool live = i < p.L;
     const float lse2 = live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
     const float delta = live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
     for (int t = 0; t < nk; ++t) {
+      const uint32_t tSh = tS + half * 64 + lane_off, tdP = tdP0 + (t & 1) * 128 + half * 64 + lane_off;
+      const int j0 = t * 128 + half * 64;
+      const bool partial = CAUSAL && j0 + 63 > i0;
+      float pr[64];
       FLB_BWAIT(sm, BB_SP_FULL, t & 1);
       tc_fence_after();
-      const int j0 = t * 128;
-      const bool partial = CAUSAL && j0 + 127 > i0;
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t s[32], dp[32], pk[16];
-        tmem_ld32_sync(tS + lane_off + c0, s);
-        tmem_ld32_sync(tdP + lane_off + c0, dp);
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t sv[32];
+        tmem_ld32_sync(tSh + c0, sv);
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float pr = ex2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -lse2));
-            float g = pr * (__uint_as_float(dp[c + e]) - delta) * p.scale;
-            if (partial && j0 + c0 + c + e > i) g = 0.f;
-            ds[e] = g;
-          }
-          pk[c >> 1] = pack_bf16(ds[0], ds[1]);
+        for (int c = 0; c < 32; ++c) {
+          float e = ex2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -lse2));
+          if (partial && j0 + c0 + c > i) e = 0.f;
+          pr[c0 + c] = e * p.scale;
         }
-        tmem_st16(tS + lane_off + (c0 >> 1), pk);  // dS (bf16) over the columns of S already read
+      }
+      tc_fence_before();
+      mbar_arrive(sm.bar(BB_S_FREE));   // the next score product may overwrite the columns
+      FLB_BWAIT(sm, BB_DP_FULL + (t & 1), (t >> 1) & 1);
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t dp[32], pk[16];
+        tmem_ld32_sync(tdP + c0, dp);
+#pragma unroll
+        for (int c = 0; c < 32; c += 2)
+          pk[c >> 1] = pack_bf16(pr[c0 + c] * (__uint_as_float(dp[c]) - delta),
+                                 pr[c0 + c + 1] * (__uint_as_float(dp[c + 1]) - delta));
+        tmem_st16(tdP + (c0 >> 1), pk);  // dS (bf16) over the thread's own dP columns
       }
       tmem_wait_st();
       tc_fence_before();
@@ -285,13 +322,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (nk > 0) {
       FLB_BWAIT(sm, BB_ACC_DONE, 0);
       tc_fence_after();
-      bwd_stage_rows<C>(tdQ + lane_off, sm.res(0), row, 1.0f);
-    } else {
-      // no key tile (cannot happen with L, S > 0): zeros
+      bwd_stage_rows<C, D / 2>(tdQ + lane_off, sm.res(0), row, half * (D / 2), 1.0f);
     }
     fence_proxy_async_smem();
-    named_bar_sync(1, 128);
-    if (row == 0 && nk > 0) {
+    named_bar_sync(1, kBwdPointwiseThreads);
+    if (threadIdx.x == 0 && nk > 0) {
 #pragma unroll
       for (int b = 0; b < C::NB; ++b)
         tma_store_4d(&tmdQ, smem_u32(sm.res(0)) + b * C::BOX_BYTES, b * 64, i0, h, n);
@@ -303,16 +338,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const uint32_t leader = elect_one() ? 1u : 0u;
     if (nk > 0) {
       FLB_BWAIT(sm, BB_RES_FULL, 0);
+      FLB_BWAIT(sm, BB_RING_FULL + 0, 0);
+      tc_fence_after();
+      bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(0, 0));                      // S(0) = Q K^T
+      umma_commit_c(leader, sm.bar(BB_SP_FULL));
+      FLB_BWAIT(sm, BB_RING2_FULL + 0, 0);
+      tc_fence_after();
+      bwd_mma_scores<C>(leader, tdP0, sm.res(1), sm.slot(0, 1));                    // dP(0) = dO V^T
+      umma_commit_c(leader, sm.bar(BB_RING2_EMPTY + 0));
+      umma_commit_c(leader, sm.bar(BB_DP_FULL + 0));
       for (int t = 0; t < nk; ++t) {
         const int slot = t % C::NSLOT;
-        FLB_BWAIT(sm, BB_RING_FULL + slot, (t / C::NSLOT) & 1);
+        if (t + 1 < nk) {
+          const int s1 = (t + 1) % C::NSLOT;
+          const uint32_t par1 = ((t + 1) / C::NSLOT) & 1;
+          FLB_BWAIT(sm, BB_RING_FULL + s1, par1);
+          FLB_BWAIT(sm, BB_S_FREE, t & 1);        // the probabilities of tile t are in registers
+          tc_fence_after();
+          bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(s1, 0));                  // S(t+1)
+          umma_commit_c(leader, sm.bar(BB_SP_FULL));
+          // the other dP buffer held dS(t-1), which the dQ product issued before this point has read
+          FLB_BWAIT(sm, BB_RING2_FULL + s1, par1);
+          tc_fence_after();
+          bwd_mma_scores<C>(leader, tdP0 + ((t + 1) & 1) * 128, sm.res(1), sm.slot(s1, 1));   // dP(t+1)
+          umma_commit_c(leader, sm.bar(BB_RING2_EMPTY + s1));
+          umma_commit_c(leader, sm.bar(BB_DP_FULL + ((t + 1) & 1)));
+        }
+        FLB_BWAIT(sm, BB_DS_FULL, t & 1);         // dS(t) written
         tc_fence_after();
-        bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(slot, 0));    // S  = Q K^T
-        bwd_mma_scores<C>(leader, tdP, sm.res(1), sm.slot(slot, 1));   // dP = dO V^T
-        umma_commit_c(leader, sm.bar(BB_SP_FULL));
-        FLB_BWAIT(sm, BB_DS_FULL, t & 1);
-        tc_fence_after();
-        bwd_mma_acc<C>(leader, tdQ, tS, sm.slot(slot, 0), t > 0);      // dQ += dS K
+        bwd_mma_acc<C>(leader, tdQ, tdP0 + (t & 1) * 128, sm.slot(slot, 0), t > 0);  // dQ += dS K
         umma_commit_c(leader, sm.bar(BB_RING_EMPTY + slot));
       }
       umma_commit_c(leader, sm.bar(BB_ACC_DONE));
@@ -325,16 +379,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       bwd_load_tile<C>(sm.res(1), &tmdO, sm.bar(BB_RES_FULL), i0, h, n);
       for (int t = 0; t < nk; ++t) {
         const int slot = t % C::NSLOT;
-        FLB_BWAIT(sm, BB_RING_EMPTY + slot, ((t / C::NSLOT) & 1) ^ 1);
-        mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), 2 * C::TILE_BYTES);
-        bwd_load_tile<C>(sm.slot(slot, 0), &tmK, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
-        bwd_load_tile<C>(sm.slot(slot, 1), &tmV, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
+        const uint32_t par = ((t / C::NSLOT) & 1) ^ 1;
+        // a slot's V half is released by dP (early), its K half by dQ (late): K first for the first
+        // tiles (their score product is what the CTA waits for), V first once the ring has wrapped
+        if (t < C::NSLOT) {
+          mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), C::TILE_BYTES);
+          bwd_load_tile<C>(sm.slot(slot, 0), &tmK, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
+          mbar_arrive_expect_tx(sm.bar(BB_RING2_FULL + slot), C::TILE_BYTES);
+          bwd_load_tile<C>(sm.slot(slot, 1), &tmV, sm.bar(BB_RING2_FULL + slot), t * 128, kvh, n);
+        } else {
+          FLB_BWAIT(sm, BB_RING2_EMPTY + slot, par);
+          mbar_arrive_expect_tx(sm.bar(BB_RING2_FULL + slot), C::TILE_BYTES);
+          bwd_load_tile<C>(sm.slot(slot, 1), &tmV, sm.bar(BB_RING2_FULL + slot), t * 128, kvh, n);
+          FLB_BWAIT(sm, BB_RING_EMPTY + slot, par);
+          mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), C::TILE_BYTES);
+          bwd_load_tile<C>(sm.slot(slot, 0), &tmK, sm.bar(BB_RING_FULL + slot), t * 128, kvh, n);
+        }
       }
     }
   };
-  if (warp < 4) pointwise();
-  else if (warp == 4) { issue(); __syncwarp(); }
-  else if (warp == 5 && lane == 0) produce();
+  if (warp < 8) pointwise();
+  else if (warp == 8) { issue(); __syncwarp(); }
+  else if (warp == 9 && lane == 0) produce();
   bwd_exit<C>(sm, p, warp);
 }
 
@@ -342,7 +408,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 // dK, dV
 // ------------------------------------------------------------------------------------------
 template <int D, bool CAUSAL>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
@@ -366,34 +432,33 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 256 + D;
 
   auto pointwise = [&]() {
-    // pointwise pass, one thread per key row; lse2 / delta of the step's 128 queries go through shared memory
-    const int row = threadIdx.x;
+    // pointwise pass: thread (row, half) owns the key row's columns (queries) [64 half, 64 half + 64);
+    // lse2 / delta of the step's 128 queries go through shared memory (the first 128 threads fetch
+    // lse2, the others delta)
+    const int row = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int j = j0 + row;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    auto fetch_vec = [&](int step, float& l2, float& dl) {
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    auto fetch_vec = [&](int step) {
       const int g = step / per_head, qt = q_lo + step % per_head;
       const int h = kvh * p.G + g, i = qt * 128 + row;
       const bool live = i < p.L;
-      l2 = live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
-      dl = live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
+      if (half == 0) return live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
+      return live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
     };
-    float nl2 = 0.f, ndl = 0.f;
-    if (steps > 0) {
-      fetch_vec(0, nl2, ndl);
-      sm.vec(0, 0)[row] = nl2;
-      sm.vec(0, 1)[row] = ndl;
-    }
+    float nv = 0.f;
+    if (steps > 0) sm.vec(0, half)[row] = fetch_vec(0);
     for (int t = 0; t < steps; ++t) {
-      if (t + 1 < steps) fetch_vec(t + 1, nl2, ndl);   // in flight while this tile is processed
+      if (t + 1 < steps) nv = fetch_vec(t + 1);        // in flight while this tile is processed
       FLB_BWAIT(sm, BB_SP_FULL, t & 1);
       tc_fence_after();
-      named_bar_sync(1, 128);                          // this step's vectors are in place
+      named_bar_sync(1, kBwdPointwiseThreads);         // this step's vectors are in place
       const int i0 = (q_lo + t % per_head) * 128;
       const bool partial = CAUSAL && j0 + 127 > i0;
       const float4* l2v = reinterpret_cast<const float4*>(sm.vec(t & 1, 0));
       const float4* dlv = reinterpret_cast<const float4*>(sm.vec(t & 1, 1));
 #pragma unroll
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
+        const int c0 = half * 64 + cc;
         uint32_t s[32], dp[32], pp[16], pd[16];
         tmem_ld32_sync(tS + lane_off + c0, s);
         tmem_ld32_sync(tdP + lane_off + c0, dp);
@@ -414,34 +479,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           pd[c >> 1] = pack_bf16(ds[0], ds[1]);
           pd[(c >> 1) + 1] = pack_bf16(ds[2], ds[3]);
         }
-        tmem_st16(tS + lane_off + (c0 >> 1), pp);    // P^T (bf16) over the columns of S^T already read
-        tmem_st16(tdP + lane_off + (c0 >> 1), pd);   // dS^T over the columns of dP^T already read
+        tmem_st16(tS + lane_off + half * 64 + (cc >> 1), pp);    // P^T (bf16) over the thread's own columns of S^T
+        tmem_st16(tdP + lane_off + half * 64 + (cc >> 1), pd);   // dS^T over its own columns of dP^T
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(sm.bar(BB_DS_FULL));
-      if (t + 1 < steps) {   // the other buffer was last read in step t - 1, before this step's barrier
-        sm.vec((t + 1) & 1, 0)[row] = nl2;
-        sm.vec((t + 1) & 1, 1)[row] = ndl;
-      }
+      // the other buffer was last read in step t - 1, before this step's barrier
+      if (t + 1 < steps) sm.vec((t + 1) & 1, half)[row] = nv;
     }
     // epilogue: dV and dK tiles -> bf16 -> shared memory (the K and V tiles are dead) -> TMA stores
     if (steps > 0) {
       FLB_BWAIT(sm, BB_ACC_DONE, 0);
       tc_fence_after();
-      bwd_stage_rows<C>(tdV + lane_off, sm.res(1), row, 1.0f);
-      bwd_stage_rows<C>(tdK + lane_off, sm.res(0), row, 1.0f);
+      if (half == 0) bwd_stage_rows<C, D>(tdV + lane_off, sm.res(1), row, 0, 1.0f);
+      else bwd_stage_rows<C, D>(tdK + lane_off, sm.res(0), row, 0, 1.0f);
     } else {
       // a key tile no query sees (causal with S > L): zeros
       const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int c = 0; c < C::TILE_BYTES / 128 / 16; ++c) {
-        reinterpret_cast<uint4*>(sm.res(0) + row * (C::TILE_BYTES / 128))[c] = z;
-        reinterpret_cast<uint4*>(sm.res(1) + row * (C::TILE_BYTES / 128))[c] = z;
-      }
+      for (int c = 0; c < C::TILE_BYTES / 128 / 16; ++c)
+        reinterpret_cast<uint4*>(sm.res(half) + row * (C::TILE_BYTES / 128))[c] = z;
     }
     fence_proxy_async_smem();
-    named_bar_sync(2, 128);
-    if (row == 0) {
+    named_bar_sync(2, kBwdPointwiseThreads);
+    if (threadIdx.x == 0) {
 #pragma unroll
       for (int b = 0; b < C::NB; ++b) {
         tma_store_4d(&tmdK, smem_u32(sm.res(0)) + b * C::BOX_BYTES, b * 64, j0, kvh, n);
@@ -486,9 +547,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   };
-  if (warp < 4) pointwise();
-  else if (warp == 4) { issue(); __syncwarp(); }
-  else if (warp == 5 && lane == 0) produce();
+  if (warp < 8) pointwise();
+  else if (warp == 8) { issue(); __syncwarp(); }
+  else if (warp == 9 && lane == 0) produce();
   bwd_exit<C>(sm, p, warp);
 }
 
