@@ -7,7 +7,7 @@
 //
 //   attn_bwd_dq_kernel      one CTA per (batch, query head, 128-row query tile); walks the key tiles:
 //                             S = Q K^T, dP = dO V^T            (tcgen05 SS products into tensor memory)
-//                             P = exp2(S * scale_log2 - lse2),  dS = P * (dP - delta) * scale
+//                             P = exp2(S * scale_log2 - lse2),  dS = P * (dP - delta)   (scale: epilogue)
 //                             dQ += dS K                         (dS read from tensor memory)
 //
 //   attn_bwd_dkv_kernel     one CTA per (batch, kv head, 128-key tile); walks the query tiles of every
@@ -289,30 +289,32 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       float pr[64];
       FLB_BWAIT(sm, BB_SP_FULL, t & 1);
       tc_fence_after();
+      {
+        uint32_t sv[64];
+        tmem_ld32_pair_sync(tSh, sv, tSh + 32, sv + 32);
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t sv[32];
-        tmem_ld32_sync(tSh + c0, sv);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 64; ++c) {
           float e = ex2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -lse2));
-          if (partial && j0 + c0 + c > i) e = 0.f;
-          pr[c0 + c] = e * p.scale;
+          if (partial && j0 + c > i) e = 0.f;
+          pr[c] = e;
         }
       }
       tc_fence_before();
       mbar_arrive(sm.bar(BB_S_FREE));   // the next score product may overwrite the columns
       FLB_BWAIT(sm, BB_DP_FULL + (t & 1), (t >> 1) & 1);
       tc_fence_after();
+      {
+        uint32_t dp[64];
+        tmem_ld32_pair_sync(tdP, dp, tdP + 32, dp + 32);
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t dp[32], pk[16];
-        tmem_ld32_sync(tdP + c0, dp);
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2)
-          pk[c >> 1] = pack_bf16(pr[c0 + c] * (__uint_as_float(dp[c]) - delta),
-                                 pr[c0 + c + 1] * (__uint_as_float(dp[c + 1]) - delta));
-        tmem_st16(tdP + (c0 >> 1), pk);  // dS (bf16) over the thread's own dP columns
+          for (int c = 0; c < 32; c += 2)
+            pk[c >> 1] = pack_bf16(pr[c0 + c] * (__uint_as_float(dp[c0 + c]) - delta),
+                                   pr[c0 + c + 1] * (__uint_as_float(dp[c0 + c + 1]) - delta));
+          tmem_st16(tdP + (c0 >> 1), pk);  // dS (bf16) over the thread's own dP columns
+        }
       }
       tmem_wait_st();
       tc_fence_before();
@@ -322,7 +324,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (nk > 0) {
       FLB_BWAIT(sm, BB_ACC_DONE, 0);
       tc_fence_after();
-      bwd_stage_rows<C, D / 2>(tdQ + lane_off, sm.res(0), row, half * (D / 2), 1.0f);
+      bwd_stage_rows<C, D / 2>(tdQ + lane_off, sm.res(0), row, half * (D / 2), p.scale);
     }
     fence_proxy_async_smem();
     named_bar_sync(1, kBwdPointwiseThreads);
@@ -460,8 +462,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int cc = 0; cc < 64; cc += 32) {
         const int c0 = half * 64 + cc;
         uint32_t s[32], dp[32], pp[16], pd[16];
-        tmem_ld32_sync(tS + lane_off + c0, s);
-        tmem_ld32_sync(tdP + lane_off + c0, dp);
+        tmem_ld32_pair_sync(tS + lane_off + c0, s, tdP + lane_off + c0, dp);
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
           const float4 l2 = l2v[(c0 + c) >> 2], dl = dlv[(c0 + c) >> 2];
@@ -472,7 +473,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             float pe = ex2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -l2a[e]));
             if (partial && j > i0 + c0 + c + e) pe = 0.f;   // key after the query
             pr[e] = pe;
-            ds[e] = pe * (__uint_as_float(dp[c + e]) - dla[e]) * p.scale;
+            ds[e] = pe * (__uint_as_float(dp[c + e]) - dla[e]);
           }
           pp[c >> 1] = pack_bf16(pr[0], pr[1]);
           pp[(c >> 1) + 1] = pack_bf16(pr[2], pr[3]);
@@ -493,7 +494,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       FLB_BWAIT(sm, BB_ACC_DONE, 0);
       tc_fence_after();
       if (half == 0) bwd_stage_rows<C, D>(tdV + lane_off, sm.res(1), row, 0, 1.0f);
-      else bwd_stage_rows<C, D>(tdK + lane_off, sm.res(0), row, 0, 1.0f);
+      else bwd_stage_rows<C, D>(tdK + lane_off, sm.res(0), row, 0, p.scale);
     } else {
       // a key tile no query sees (causal with S > L): zeros
       const uint4 z = make_uint4(0, 0, 0, 0);
