@@ -263,9 +263,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   BwdSmem<C> sm{reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023))};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.L + 127) / 128;
-  // heaviest (latest) query tiles first under the causal mask
-  const int qt = nq - 1 - static_cast<int>(blockIdx.x) / (p.N * p.Hq);
-  const int nh = static_cast<int>(blockIdx.x) % (p.N * p.Hq);
+  // consecutive CTAs take the query tiles of one (batch, head), latest (heaviest under the causal mask)
+  // first: the CTAs in flight then share a few heads' K and V, which stay in L2
+  const int qt = nq - 1 - static_cast<int>(blockIdx.x) % nq;
+  const int nh = static_cast<int>(blockIdx.x) / nq;
   const int n = nh / p.Hq, h = nh % p.Hq, kvh = h / p.G;
   const int i0 = qt * 128;
   const int nk_all = (p.S + 127) / 128;
@@ -419,9 +420,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   BwdSmem<C> sm{reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023))};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.L + 127) / 128;
-  // the first key tiles see the most queries under the causal mask: block order is already heaviest first
-  const int kt = static_cast<int>(blockIdx.x) / (p.N * p.Hkv);
-  const int nh = static_cast<int>(blockIdx.x) % (p.N * p.Hkv);
+  // consecutive CTAs take the key tiles of one (batch, kv head), first (heaviest under the causal mask)
+  // first: the CTAs in flight then stream the same few heads' Q and dO, which stay in L2
+  const int nkt = (p.S + 127) / 128;
+  const int kt = static_cast<int>(blockIdx.x) % nkt;
+  const int nh = static_cast<int>(blockIdx.x) / nkt;
   const int n = nh / p.Hkv, kvh = nh % p.Hkv;
   const int j0 = kt * 128;
   const int q_lo = CAUSAL ? min(nq, j0 / 128) : 0;   // first query tile with a row i >= j0
