@@ -283,21 +283,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const bool live = i < p.L;
     const float lse2 = live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
     const float delta = live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
+    const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), nlse2 = make_float2(-lse2, -lse2);
+    const float2 ndelta2 = make_float2(-delta, -delta);
     for (int t = 0; t < nk; ++t) {
       const uint32_t tSh = tS0 + (t & 1) * 128 + half * 64 + lane_off, tdP = tdP0 + half * 64 + lane_off;
       const int j0 = t * 128 + half * 64;
       const bool partial = CAUSAL && j0 + 63 > i0;
-      float pr[64];
+      float2 pr[32];
       FLB_BWAIT(sm, BB_SP_FULL + (t & 1), (t >> 1) & 1);
       tc_fence_after();
       {
         uint32_t sv[64];
         tmem_ld32_pair_sync(tSh, sv, tSh + 32, sv + 32);
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float e = ex2(fmaf(__uint_as_float(sv[c]), p.scale_log2, -lse2));
-          if (partial && j0 + c > i) e = 0.f;
-          pr[c] = e;
+        for (int c = 0; c < 64; c += 2) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nlse2);
+          float2 e = make_float2(ex2(x.x), ex2(x.y));
+          if (partial) {
+            if (j0 + c > i) e.x = 0.f;
+            if (j0 + c + 1 > i) e.y = 0.f;
+          }
+          pr[c >> 1] = e;
         }
       }
       FLB_BWAIT(sm, BB_DP_FULL, t & 1);
@@ -309,9 +315,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 32; c += 2)
-            pk[c >> 1] = pack_bf16(pr[c0 + c] * (__uint_as_float(dp[c0 + c]) - delta),
-                                   pr[c0 + c + 1] * (__uint_as_float(dp[c0 + c + 1]) - delta));
+          for (int c = 0; c < 32; c += 2) {
+            const float2 d = __fadd2_rn(make_float2(__uint_as_float(dp[c0 + c]), __uint_as_float(dp[c0 + c + 1])), ndelta2);
+            const float2 g = __fmul2_rn(pr[(c0 + c) >> 1], d);
+            pk[c >> 1] = pack_bf16(g.x, g.y);
+          }
           tmem_st16(tSh + (c0 >> 1), pk);  // dS (bf16) over the thread's own score columns
         }
       }
@@ -452,6 +460,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       return live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
     };
     float nv = 0.f;
+    const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     if (steps > 0) sm.vec(0, half)[row] = fetch_vec(0);
     for (int t = 0; t < steps; ++t) {
       if (t + 1 < steps) nv = fetch_vec(t + 1);        // in flight while this tile is processed
@@ -462,26 +471,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const bool partial = CAUSAL && j0 + 127 > i0;
       const float4* l2v = reinterpret_cast<const float4*>(sm.vec(t & 1, 0)) + half * 16;
       const float4* dlv = reinterpret_cast<const float4*>(sm.vec(t & 1, 1)) + half * 16;
-      float pr[64];
+      float2 pr[32];
       {
         uint32_t sv[64];
         tmem_ld32_pair_sync(tSh, sv, tSh + 32, sv + 32);
 #pragma unroll
         for (int c = 0; c < 64; c += 4) {
           const float4 l2 = l2v[c >> 2];
-          const float l2a[4] = {l2.x, l2.y, l2.z, l2.w};
+          const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2,
+                                       make_float2(-l2.x, -l2.y));
+          const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2,
+                                       make_float2(-l2.z, -l2.w));
+          float pe[4] = {ex2(xa.x), ex2(xa.y), ex2(xb.x), ex2(xb.y)};
+          if (partial) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pe = ex2(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -l2a[e]));
-            if (partial && j > i0 + c + e) pe = 0.f;   // key after the query
-            pr[c + e] = pe;
+            for (int e = 0; e < 4; ++e)
+              if (j > i0 + c + e) pe[e] = 0.f;   // key after the query
           }
+          pr[c >> 1] = make_float2(pe[0], pe[1]);
+          pr[(c >> 1) + 1] = make_float2(pe[2], pe[3]);
         }
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 32; c += 2) pk[c >> 1] = pack_bf16(pr[c0 + c], pr[c0 + c + 1]);
+          for (int c = 0; c < 32; c += 2) pk[c >> 1] = pack_bf16(pr[(c0 + c) >> 1].x, pr[(c0 + c) >> 1].y);
           tmem_st16(tSh + (c0 >> 1), pk);              // P^T (bf16) over the thread's own columns of S^T
         }
       }
@@ -499,10 +513,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
             const float4 dl = dlv[(c0 + c) >> 2];
-            pk[c >> 1] = pack_bf16(pr[c0 + c] * (__uint_as_float(dp[c0 + c]) - dl.x),
-                                   pr[c0 + c + 1] * (__uint_as_float(dp[c0 + c + 1]) - dl.y));
-            pk[(c >> 1) + 1] = pack_bf16(pr[c0 + c + 2] * (__uint_as_float(dp[c0 + c + 2]) - dl.z),
-                                         pr[c0 + c + 3] * (__uint_as_float(dp[c0 + c + 3]) - dl.w));
+            const float2 da = __fadd2_rn(make_float2(__uint_as_float(dp[c0 + c]), __uint_as_float(dp[c0 + c + 1])),
+                                         make_float2(-dl.x, -dl.y));
+            const float2 db = __fadd2_rn(make_float2(__uint_as_float(dp[c0 + c + 2]), __uint_as_float(dp[c0 + c + 3])),
+                                         make_float2(-dl.z, -dl.w));
+            const float2 ga = __fmul2_rn(pr[(c0 + c) >> 1], da), gb = __fmul2_rn(pr[((c0 + c) >> 1) + 1], db);
+            pk[c >> 1] = pack_bf16(ga.x, ga.y);
+            pk[(c >> 1) + 1] = pack_bf16(gb.x, gb.y);
           }
           tmem_st16(tdPh + (c0 >> 1), pk);             // dS^T over the thread's own columns of dP^T
         }
