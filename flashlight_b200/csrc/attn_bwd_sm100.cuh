@@ -62,6 +62,13 @@ enum : int {
 };
 static_assert(BB_COUNT * 8 <= 256, "the barriers end where the tensor-memory base word begins");
 constexpr int kBwdPointwiseThreads = 256;
+// of every kBwdPolyPeriod column pairs, kBwdPolyCount take their exponentials from the FMA-pipe polynomial
+// (none, one in four and one in two measured within 3 % of each other)
+constexpr int kBwdPolyPeriod = 4, kBwdPolyCount = 1;
+FLB_DEV float2 bwd_exp2_pair(float2 x, int pair) {
+  if (pair % kBwdPolyPeriod < kBwdPolyCount) return exp2_poly2(x);
+  return make_float2(ex2(x.x), ex2(x.y));
+}
 constexpr int kBwdThreads = kBwdPointwiseThreads + 64;
 
 template <int D_>
@@ -298,7 +305,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
         for (int c = 0; c < 64; c += 2) {
           const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2, nlse2);
-          float2 e = make_float2(ex2(x.x), ex2(x.y));
+          float2 e = bwd_exp2_pair(x, c >> 1);
           if (partial) {
             if (j0 + c > i) e.x = 0.f;
             if (j0 + c + 1 > i) e.y = 0.f;
@@ -482,7 +489,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                        make_float2(-l2.x, -l2.y));
           const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2,
                                        make_float2(-l2.z, -l2.w));
-          float pe[4] = {ex2(xa.x), ex2(xa.y), ex2(xb.x), ex2(xb.y)};
+          const float2 ea = bwd_exp2_pair(xa, c >> 1), eb = bwd_exp2_pair(xb, (c >> 1) + 1);
+          float pe[4] = {ea.x, ea.y, eb.x, eb.y};
           if (partial) {
 #pragma unroll
             for (int e = 0; e < 4; ++e)

@@ -596,26 +596,6 @@ constexpr float kSpeculateSumLimit = 1024.0f;
 // largest (score / cap)^2 for which the softcap's tanh is taken from its odd polynomial
 constexpr float kSoftcapPolyLimit = 0.09f;
 
-// 2^x for a pair of non-positive-ish arguments on the FMA pipe, to take load off the
-// transcendental unit (16 ex2 per clock and SM would otherwise bound the kernel).
-// x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 minimax polynomial
-// (relative error 7.5e-5, far below the bf16 rounding of P), n added into the exponent bits.
-FLB_DEV float2 exp2_poly2(float2 x) {
-  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  constexpr float c0 = 0.99992806f, c1 = 0.69326097f, c2 = 0.24261113f, c3 = 0.05517166f;
-  x.x = fmaxf(x.x, -125.f);
-  x.y = fmaxf(x.y, -125.f);
-  const float2 r = __fadd2_rn(x, make_float2(kMagic, kMagic));
-  const float2 n = __fadd2_rn(r, make_float2(-kMagic, -kMagic));
-  const float2 f = __ffma2_rn(n, make_float2(-1.f, -1.f), x);
-  float2 q = __ffma2_rn(make_float2(c3, c3), f, make_float2(c2, c2));
-  q = __ffma2_rn(q, f, make_float2(c1, c1));
-  q = __ffma2_rn(q, f, make_float2(c0, c0));
-  q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23));
-  q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23));
-  return q;
-}
-
 // Register budgets after the roles split (setmaxnreg; 8 softmax warps, 4 epilogue warps, 4 warps
 // around the MMA and TMA issuers: 256 * softmax + 128 * epilogue + 128 * issue <= 65536)
 constexpr int kRegsSoftmax = 192, kRegsEpilogue = 64, kRegsIssue = 64;
