@@ -49,7 +49,7 @@ template <int D, bool CAUSAL>
 cudaError_t launch_bwd(const flb200_attn_bwd_params* p, const BwdParams& bp, const CUtensorMap& tmQ,
                        const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmdO,
                        const CUtensorMap& tmdQ, const CUtensorMap& tmdK, const CUtensorMap& tmdV,
-                       cudaStream_t stream) {
+                       const CUtensorMap& tmX, const CUtensorMap& tmY, cudaStream_t stream) {
   using C = BwdCfg<D>;
   auto dq = attn_bwd_dq_kernel<D, CAUSAL>;
   auto dkv = attn_bwd_dkv_kernel<D, CAUSAL>;
@@ -58,7 +58,7 @@ cudaError_t launch_bwd(const flb200_attn_bwd_params* p, const BwdParams& bp, con
   e = cudaFuncSetAttribute(dkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   if (e != cudaSuccess) return e;
   const int nq = (p->L + 127) / 128, nk = (p->S + 127) / 128;
-  dkv<<<nk * p->N * p->Hkv, kBwdThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdK, tmdV, bp);
+  dkv<<<nk * p->N * p->Hkv, kBwdThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdK, tmdV, tmX, tmY, bp);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dq<<<nq * p->N * p->Hq, kBwdThreads, C::SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmdO, tmdQ, bp);
@@ -71,8 +71,9 @@ extern "C" {
 
 size_t flb200_attn_bwd_workspace_bytes(const flb200_attn_bwd_params* p) {
   if (!p || p->struct_size != sizeof(flb200_attn_bwd_params) || p->N <= 0 || p->Hq <= 0 || p->L <= 0) return 0;
+  // per padded query row: delta (fp32), then the two 16-column bf16 rows of the dK/dV kernel's extra k-step
   const size_t lp = (static_cast<size_t>(p->L) + 127) / 128 * 128;
-  return static_cast<size_t>(p->N) * p->Hq * lp * sizeof(float);
+  return static_cast<size_t>(p->N) * p->Hq * lp * (sizeof(float) + 2 * 32);
 }
 
 int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
@@ -110,7 +111,7 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
 
   // head dims below a built width run on it: the tensor maps zero-fill the missing feature columns
   const int width = p->E <= 64 ? 64 : 128;
-  CUtensorMap tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV;
+  CUtensorMap tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, tmX, tmY;
   auto map = [&](CUtensorMap* tm, const void* base, int rows, int heads, const int64_t* st) {
     return make_tmap_bf16_4d(tm, base, p->E, rows, heads, p->N, st[2], st[1], st[0], 64, 128);
   };
@@ -121,18 +122,25 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
     return FLB200_E_LAUNCH;
 
   const int rows = p->N * p->Hq * bp.Lp;
+  uint8_t* xrows = static_cast<uint8_t*>(p->workspace) + static_cast<size_t>(rows) * sizeof(float);
+  uint8_t* yrows = xrows + static_cast<size_t>(rows) * 32;
+  const uint64_t lp = static_cast<uint64_t>(bp.Lp);
+  if (make_tmap_bf16_4d(&tmX, xrows, 16, lp, p->Hq, p->N, 16, lp * 16, lp * 16 * p->Hq, 16, 128) ||
+      make_tmap_bf16_4d(&tmY, yrows, 16, lp, p->Hq, p->N, 16, lp * 16, lp * 16 * p->Hq, 16, 128))
+    return FLB200_E_LAUNCH;
   attn_bwd_delta_kernel<<<rows / 16, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->dout), p->o_stride[0],
       p->o_stride[1], p->o_stride[2], p->do_stride[0], p->do_stride[1], p->do_stride[2], p->E, p->Hq, p->L, bp.Lp,
-      bp.delta);
+      bp.delta, p->lse, p->lse_stride[0], p->lse_stride[1], 1.0f / p->scale, reinterpret_cast<uint4*>(xrows),
+      reinterpret_cast<uint4*>(yrows));
   if (cudaGetLastError() != cudaSuccess) return FLB200_E_LAUNCH;
   cudaError_t e;
   if (width == 64)
-    e = p->causal ? launch_bwd<64, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream)
-                  : launch_bwd<64, false>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream);
+    e = p->causal ? launch_bwd<64, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, tmX, tmY, stream)
+                  : launch_bwd<64, false>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, tmX, tmY, stream);
   else
-    e = p->causal ? launch_bwd<128, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream)
-                  : launch_bwd<128, false>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, stream);
+    e = p->causal ? launch_bwd<128, true>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, tmX, tmY, stream)
+                  : launch_bwd<128, false>(p, bp, tmQ, tmK, tmV, tmdO, tmdQ, tmdK, tmdV, tmX, tmY, stream);
   if (e != cudaSuccess) return FLB200_E_LAUNCH;
   flb::count_launches(3);
   return FLB200_OK;

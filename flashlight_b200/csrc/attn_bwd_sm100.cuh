@@ -15,6 +15,12 @@
 //                           (tensor-memory lanes are keys):
 //                             S^T = K Q^T, dP^T = V dO^T;  P^T, dS^T as above (lse2, delta per column)
 //                             dV += P^T dO,  dK += dS^T Q
+//                           Here lse2 and delta belong to the columns, and reading 128 of them per thread
+//                           and step from shared memory cost as much as the exponentials.  The tensor
+//                           cores subtract them instead: the delta kernel also writes, per query row,
+//                           x = -lse / scale and y = -delta as two bf16 terms each (16-column rows
+//                           [hi, lo, 0...]), and each score product takes one more k-step of 16 against a
+//                           resident tile of ones: S^T + x_i = (s - lse / scale), dP^T + y_i = dP - delta.
 //
 // The score products are recomputed in both kernels (7 tile products per pair of tiles instead of 5);
 // in exchange every accumulator stays in one CTA's tensor memory from start to finish.
@@ -82,7 +88,9 @@ struct BwdCfg {
   static constexpr int NSLOT = D == 128 ? 2 : 4;
   static constexpr int VEC_BYTES = 2 * 2 * 128 * 4;  // lse2 / delta of the step's 128 queries, two buffers
   static constexpr int AUX_BYTES = 1024;
-  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSLOT * SLOT_BYTES + VEC_BYTES + AUX_BYTES;
+  static constexpr int AUG_TILE_BYTES = 128 * 16 * 2;  // 128 rows of 16 bf16, 32-byte swizzled
+  static constexpr int AUG_BYTES = AUG_TILE_BYTES * (1 + 2 * NSLOT);   // ones, then (x, y) per ring slot
+  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSLOT * SLOT_BYTES + VEC_BYTES + AUX_BYTES + AUG_BYTES;
   static_assert(SMEM_BYTES > 120 * 1024, "one CTA per SM: each takes all of tensor memory");
 };
 
@@ -95,6 +103,8 @@ struct BwdSmem {
     return reinterpret_cast<float*>(base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES) + (buf * 2 + which) * 128;
   }
   FLB_DEV uint8_t* aux() const { return base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES + C::VEC_BYTES; }
+  FLB_DEV uint8_t* ones() const { return aux() + C::AUX_BYTES; }
+  FLB_DEV uint8_t* aug(int s, int i) const { return ones() + C::AUG_TILE_BYTES * (1 + 2 * s + i); }  // x: 0, y: 1
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
   FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 256); }  // after BB_COUNT barriers
   FLB_DEV WaitCtl* ctl() const { return reinterpret_cast<WaitCtl*>(aux() + 260); }
@@ -136,6 +146,16 @@ FLB_DEV void bwd_mma_scores(uint32_t leader, uint32_t d_tmem, const void* a_tile
     const uint32_t off = ((kk / 64) * C::BOX_BYTES + (kk % 64) * 2) >> 4;
     umma_ss_c<1>(leader, d_tmem, a + off, b + off, Ds::k_hi, idesc);
   }
+}
+
+// D[tmem 128 x 128] += A[128 x 16] * B[128 x 16]^T, both K-major tiles of 32-byte swizzled rows
+template <class C>
+FLB_DEV void bwd_mma_aug(uint32_t leader, uint32_t d_tmem, const void* a_tile, const void* b_tile) {
+  constexpr uint64_t d32 = (static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 16) | (1ull << 46) |
+                           (static_cast<uint64_t>(kSwz32) << 61);
+  constexpr uint32_t hi = static_cast<uint32_t>(d32 >> 32), lo = static_cast<uint32_t>(d32);
+  constexpr uint32_t idesc = make_idesc_bf16(128, 128, 0, 0);
+  umma_ss_c<1>(leader, d_tmem, lo + BwdDesc<C>::addr(a_tile), lo + BwdDesc<C>::addr(b_tile), hi, idesc);
 }
 
 // D[tmem 128 x D] (+)= A[tmem 128 x 128, bf16] * B[128 x D], B an MN-major tile in shared memory.  The A
@@ -226,9 +246,19 @@ FLB_DEV void bwd_exit(const BwdSmem<C>& sm, const BwdParams& p, int warp) {
 // ------------------------------------------------------------------------------------------
 // delta[n][h][i] = sum_d dO * O   (rows beyond L of the padded array: 0)
 // ------------------------------------------------------------------------------------------
+// hi + lo = v to about 16 bits; a non-finite v gives (-inf, 0): the exponential of such a row's scores is 0
+FLB_DEV uint32_t bwd_split_bf16(float v) {
+  if (!(fabsf(v) <= 3.0e38f)) return 0xFF80u;
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+  return static_cast<uint32_t>(__bfloat16_as_ushort(hi)) | (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
+}
+
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       int64_t o_sn, int64_t o_sh, int64_t o_sl, int64_t do_sn, int64_t do_sh,
-                                      int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta) {
+                                      int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta,
+                                      const float* __restrict__ lse, int64_t lse_sn, int64_t lse_sh, float inv_scale,
+                                      uint4* __restrict__ xrows, uint4* __restrict__ yrows) {
   // 16 lanes per (n, h, i) row, 8 features (one 16-byte load per tensor) per lane; rows start on 16-byte
   // boundaries (pointers and strides are checked by the host)
   const int row = blockIdx.x * 16 + (threadIdx.x >> 4);
@@ -254,7 +284,18 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const
   }
 #pragma unroll
   for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (sub == 0) delta[row] = acc;
+  // the rows of the extra k-step of the dK/dV kernel: [hi, lo, 0 x 14] of -lse / scale and of -delta
+  // (rows of the padding beyond L: zeros; their Q and dO rows are zero-filled, so they contribute nothing)
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  if (sub == 0) {
+    delta[row] = acc;
+    yrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? bwd_split_bf16(-acc) : 0u, 0, 0, 0);
+    yrows[2 * static_cast<int64_t>(row) + 1] = zero;
+  } else if (sub == 1) {
+    const float x = i < L ? -lse[n * lse_sn + h * lse_sh + i] * inv_scale : 0.f;
+    xrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? bwd_split_bf16(x) : 0u, 0, 0, 0);
+    xrows[2 * static_cast<int64_t>(row) + 1] = zero;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -429,6 +470,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                     const __grid_constant__ CUtensorMap tmdK, const __grid_constant__ CUtensorMap tmdV,
+                    const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                     const __grid_constant__ BwdParams p) {
   using C = BwdCfg<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -445,6 +487,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int q_lo = CAUSAL ? min(nq, j0 / 128) : 0;   // first query tile with a row i >= j0
   const int per_head = nq - q_lo;
   const int steps = per_head * p.G;                  // (query head of the group, query tile) pairs
+  // the resident A operand of the extra k-step: rows [1, 1, 0 x 6 | 1, 1, 0 x 6] (both 16-byte chunks
+  // alike, so the 32-byte swizzle leaves the tile as written); against a row [hi, lo, 0 x 14] it adds hi + lo
+  if (threadIdx.x < 128) {
+    uint4* r = reinterpret_cast<uint4*>(sm.ones() + threadIdx.x * 32);
+    r[0] = make_uint4(0x3F803F80u, 0, 0, 0);
+    r[1] = make_uint4(0x3F803F80u, 0, 0, 0);
+    fence_proxy_async_smem();
+  }
   bwd_setup<C>(sm, p, warp, lane);
   const uint32_t tmem = *sm.tmem_base();
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 256 + D;
@@ -453,51 +503,31 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // works under both:  P^T written -> dV += P^T dO, then S^T of the next step;
   //                    dS^T written -> dK += dS^T Q, then dP^T of the next step.
   auto pointwise = [&]() {
-    // thread (row, half) owns the key row's columns (queries) [64 half, 64 half + 64); lse2 / delta of
-    // the step's 128 queries go through shared memory (the first 128 threads fetch lse2, the others delta)
+    // thread (row, half) owns the key row's columns (queries) [64 half, 64 half + 64)
     const int row = threadIdx.x & 127, half = threadIdx.x >> 7;
     const int j = j0 + row;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tSh = tS + lane_off + half * 64, tdPh = tdP + lane_off + half * 64;
-    auto fetch_vec = [&](int step) {
-      const int g = step / per_head, qt = q_lo + step % per_head;
-      const int h = kvh * p.G + g, i = qt * 128 + row;
-      const bool live = i < p.L;
-      if (half == 0) return live ? p.lse[n * p.lse_sn + h * p.lse_sh + i] * 1.4426950408889634f : CUDART_INF_F;
-      return live ? p.delta[(static_cast<int64_t>(n) * p.Hq + h) * p.Lp + i] : 0.f;
-    };
-    float nv = 0.f;
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-    if (steps > 0) sm.vec(0, half)[row] = fetch_vec(0);
     for (int t = 0; t < steps; ++t) {
-      if (t + 1 < steps) nv = fetch_vec(t + 1);        // in flight while this tile is processed
       FLB_BWAIT(sm, BB_SP_FULL, t & 1);
       tc_fence_after();
-      named_bar_sync(1, kBwdPointwiseThreads);         // this step's vectors are in place
       const int i0 = (q_lo + t % per_head) * 128 + half * 64;   // first query of the thread's columns
       const bool partial = CAUSAL && j0 + 127 > i0;
-      const float4* l2v = reinterpret_cast<const float4*>(sm.vec(t & 1, 0)) + half * 16;
-      const float4* dlv = reinterpret_cast<const float4*>(sm.vec(t & 1, 1)) + half * 16;
       float2 pr[32];
       {
         uint32_t sv[64];
         tmem_ld32_pair_sync(tSh, sv, tSh + 32, sv + 32);
 #pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-          const float4 l2 = l2v[c >> 2];
-          const float2 xa = __ffma2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2,
-                                       make_float2(-l2.x, -l2.y));
-          const float2 xb = __ffma2_rn(make_float2(__uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3])), scale2,
-                                       make_float2(-l2.z, -l2.w));
-          const float2 ea = bwd_exp2_pair(xa, c >> 1), eb = bwd_exp2_pair(xb, (c >> 1) + 1);
-          float pe[4] = {ea.x, ea.y, eb.x, eb.y};
+        for (int c = 0; c < 64; c += 2) {
+          // the score columns arrive as s - lse / scale
+          const float2 x = __fmul2_rn(make_float2(__uint_as_float(sv[c]), __uint_as_float(sv[c + 1])), scale2);
+          float2 e = bwd_exp2_pair(x, c >> 1);
           if (partial) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (j > i0 + c + e) pe[e] = 0.f;   // key after the query
+            if (j > i0 + c) e.x = 0.f;   // key after the query
+            if (j > i0 + c + 1) e.y = 0.f;
           }
-          pr[c >> 1] = make_float2(pe[0], pe[1]);
-          pr[(c >> 1) + 1] = make_float2(pe[2], pe[3]);
+          pr[c >> 1] = e;
         }
 #pragma unroll
         for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -519,15 +549,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t pk[16];
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const float4 dl = dlv[(c0 + c) >> 2];
-            const float2 da = __fadd2_rn(make_float2(__uint_as_float(dp[c0 + c]), __uint_as_float(dp[c0 + c + 1])),
-                                         make_float2(-dl.x, -dl.y));
-            const float2 db = __fadd2_rn(make_float2(__uint_as_float(dp[c0 + c + 2]), __uint_as_float(dp[c0 + c + 3])),
-                                         make_float2(-dl.z, -dl.w));
-            const float2 ga = __fmul2_rn(pr[(c0 + c) >> 1], da), gb = __fmul2_rn(pr[((c0 + c) >> 1) + 1], db);
-            pk[c >> 1] = pack_bf16(ga.x, ga.y);
-            pk[(c >> 1) + 1] = pack_bf16(gb.x, gb.y);
+          for (int c = 0; c < 32; c += 2) {
+            // the dP columns arrive as dP - delta
+            const float2 g = __fmul2_rn(pr[(c0 + c) >> 1],
+                                        make_float2(__uint_as_float(dp[c0 + c]), __uint_as_float(dp[c0 + c + 1])));
+            pk[c >> 1] = pack_bf16(g.x, g.y);
           }
           tmem_st16(tdPh + (c0 >> 1), pk);             // dS^T over the thread's own columns of dP^T
         }
@@ -535,8 +561,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(sm.bar(BB_DS_FULL));
-      // the other buffer was last read in step t - 1, before this step's barrier
-      if (t + 1 < steps) sm.vec((t + 1) & 1, half)[row] = nv;
     }
     // epilogue: dV and dK tiles -> bf16 -> shared memory (the K and V tiles are dead) -> TMA stores
     if (steps > 0) {
@@ -569,10 +593,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       FLB_BWAIT(sm, BB_RING_FULL + 0, 0);
       tc_fence_after();
       bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(0, 0));          // S^T(0) = K Q^T
+      bwd_mma_aug<C>(leader, tS, sm.ones(), sm.aug(0, 0));              //   - lse / scale per column
       umma_commit_c(leader, sm.bar(BB_SP_FULL));
       FLB_BWAIT(sm, BB_RING2_FULL + 0, 0);
       tc_fence_after();
       bwd_mma_scores<C>(leader, tdP, sm.res(1), sm.slot(0, 1));         // dP^T(0) = V dO^T
+      bwd_mma_aug<C>(leader, tdP, sm.ones(), sm.aug(0, 1));             //   - delta per column
       umma_commit_c(leader, sm.bar(BB_DP_FULL));
       for (int t = 0; t < steps; ++t) {
         const int slot = t % C::NSLOT, s1 = (t + 1) % C::NSLOT;
@@ -585,6 +611,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           FLB_BWAIT(sm, BB_RING_FULL + s1, par1);
           tc_fence_after();
           bwd_mma_scores<C>(leader, tS, sm.res(0), sm.slot(s1, 0));     // S^T(t+1), after dV has read P^T(t)
+          bwd_mma_aug<C>(leader, tS, sm.ones(), sm.aug(s1, 0));
           umma_commit_c(leader, sm.bar(BB_SP_FULL));
         }
         FLB_BWAIT(sm, BB_DS_FULL, t & 1);
@@ -595,11 +622,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           FLB_BWAIT(sm, BB_RING2_FULL + s1, par1);
           tc_fence_after();
           bwd_mma_scores<C>(leader, tdP, sm.res(1), sm.slot(s1, 1));    // dP^T(t+1), after dK has read dS^T(t)
+          bwd_mma_aug<C>(leader, tdP, sm.ones(), sm.aug(s1, 1));
           umma_commit_c(leader, sm.bar(BB_DP_FULL));
         }
       }
       umma_commit_c(leader, sm.bar(BB_ACC_DONE));
     }
+  };
+  // a step's Q tile travels with its x rows, its dO tile with its y rows
+  auto load_q = [&](int slot, int i0, int h) {
+    mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), C::TILE_BYTES + C::AUG_TILE_BYTES);
+    bwd_load_tile<C>(sm.slot(slot, 0), &tmQ, sm.bar(BB_RING_FULL + slot), i0, h, n);
+    tma_load_4d(smem_u32(sm.aug(slot, 0)), &tmX, sm.bar(BB_RING_FULL + slot), 0, i0, h, n);
+  };
+  auto load_do = [&](int slot, int i0, int h) {
+    mbar_arrive_expect_tx(sm.bar(BB_RING2_FULL + slot), C::TILE_BYTES + C::AUG_TILE_BYTES);
+    bwd_load_tile<C>(sm.slot(slot, 1), &tmdO, sm.bar(BB_RING2_FULL + slot), i0, h, n);
+    tma_load_4d(smem_u32(sm.aug(slot, 1)), &tmY, sm.bar(BB_RING2_FULL + slot), 0, i0, h, n);
   };
   auto produce = [&]() {
     if (steps > 0) {
@@ -612,17 +651,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int h = kvh * p.G + t / per_head, i0 = (q_lo + t % per_head) * 128;
         // a slot's dO half is released by dV (early), its Q half by dK (late)
         if (t < C::NSLOT) {
-          mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), C::TILE_BYTES);
-          bwd_load_tile<C>(sm.slot(slot, 0), &tmQ, sm.bar(BB_RING_FULL + slot), i0, h, n);
-          mbar_arrive_expect_tx(sm.bar(BB_RING2_FULL + slot), C::TILE_BYTES);
-          bwd_load_tile<C>(sm.slot(slot, 1), &tmdO, sm.bar(BB_RING2_FULL + slot), i0, h, n);
+          load_q(slot, i0, h);
+          load_do(slot, i0, h);
         } else {
           FLB_BWAIT(sm, BB_RING2_EMPTY + slot, par);
-          mbar_arrive_expect_tx(sm.bar(BB_RING2_FULL + slot), C::TILE_BYTES);
-          bwd_load_tile<C>(sm.slot(slot, 1), &tmdO, sm.bar(BB_RING2_FULL + slot), i0, h, n);
+          load_do(slot, i0, h);
           FLB_BWAIT(sm, BB_RING_EMPTY + slot, par);
-          mbar_arrive_expect_tx(sm.bar(BB_RING_FULL + slot), C::TILE_BYTES);
-          bwd_load_tile<C>(sm.slot(slot, 0), &tmQ, sm.bar(BB_RING_FULL + slot), i0, h, n);
+          load_q(slot, i0, h);
         }
       }
     }
