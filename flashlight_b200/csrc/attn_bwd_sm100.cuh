@@ -86,11 +86,10 @@ struct BwdCfg {
   static constexpr int TILE_BYTES = 128 * D * 2;
   static constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // a ring slot holds the step's two streamed tiles
   static constexpr int NSLOT = D == 128 ? 2 : 4;
-  static constexpr int VEC_BYTES = 2 * 2 * 128 * 4;  // lse2 / delta of the step's 128 queries, two buffers
   static constexpr int AUX_BYTES = 1024;
   static constexpr int AUG_TILE_BYTES = 128 * 16 * 2;  // 128 rows of 16 bf16, 32-byte swizzled
   static constexpr int AUG_BYTES = AUG_TILE_BYTES * (1 + 2 * NSLOT);   // ones, then (x, y) per ring slot
-  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSLOT * SLOT_BYTES + VEC_BYTES + AUX_BYTES + AUG_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + 2 * TILE_BYTES + NSLOT * SLOT_BYTES + AUX_BYTES + AUG_BYTES;
   static_assert(SMEM_BYTES > 120 * 1024, "one CTA per SM: each takes all of tensor memory");
 };
 
@@ -99,10 +98,7 @@ struct BwdSmem {
   uint8_t* base;
   FLB_DEV uint8_t* res(int i) const { return base + i * C::TILE_BYTES; }  // resident tile 0 / 1
   FLB_DEV uint8_t* slot(int s, int i) const { return base + 2 * C::TILE_BYTES + s * C::SLOT_BYTES + i * C::TILE_BYTES; }
-  FLB_DEV float* vec(int buf, int which) const {
-    return reinterpret_cast<float*>(base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES) + (buf * 2 + which) * 128;
-  }
-  FLB_DEV uint8_t* aux() const { return base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES + C::VEC_BYTES; }
+  FLB_DEV uint8_t* aux() const { return base + 2 * C::TILE_BYTES + C::NSLOT * C::SLOT_BYTES; }
   FLB_DEV uint8_t* ones() const { return aux() + C::AUX_BYTES; }
   FLB_DEV uint8_t* aug(int s, int i) const { return ones() + C::AUG_TILE_BYTES * (1 + 2 * s + i); }  // x: 0, y: 1
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }

@@ -169,3 +169,52 @@ def test_launch_without_device_fails_cleanly(lib):
     rc = lib.flb200_attn_fwd(C.byref(good()), None)
     assert rc in (_lib.E_LAUNCH, _lib.E_ARCH)
     assert lib.flb200_launch_count() == before
+
+
+def good_bwd(**over):
+    p = _lib.AttnBwdParams()
+    p.struct_size = C.sizeof(_lib.AttnBwdParams)
+    p.N, p.Hq, p.Hkv, p.L, p.S, p.E = 2, 8, 2, 300, 300, 128
+    for name in ("q", "k", "v", "o", "dout", "lse", "dq", "dk", "dv"):
+        setattr(p, name, FAKE)
+    for name, heads in (("q_stride", 8), ("o_stride", 8), ("do_stride", 8), ("dq_stride", 8),
+                        ("k_stride", 2), ("v_stride", 2), ("dk_stride", 2), ("dv_stride", 2)):
+        a = getattr(p, name)
+        a[0], a[1], a[2] = heads * 300 * 128, 300 * 128, 128
+    p.lse_stride[0], p.lse_stride[1] = 8 * 300, 300
+    p.scale = 0.088
+    p.workspace, p.workspace_bytes = FAKE, 1 << 30
+    for k, v in over.items():
+        if isinstance(v, tuple):
+            arr = getattr(p, k)
+            for i, x in enumerate(v):
+                arr[i] = x
+        else:
+            setattr(p, k, v)
+    return p
+
+
+def test_backward_workspace_is_delta_plus_the_two_rows_of_the_extra_k_step(lib):
+    lib.flb200_attn_bwd_workspace_bytes.restype = C.c_size_t
+    # 300 query rows pad to 384; per padded row an fp32 delta and two rows of 16 bf16
+    assert lib.flb200_attn_bwd_workspace_bytes(C.byref(good_bwd())) == 2 * 8 * 384 * (4 + 64)
+    assert lib.flb200_attn_bwd_workspace_bytes(None) == 0
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(struct_size=8), _lib.E_BAD_ARG),
+    (dict(Hkv=3), _lib.E_BAD_ARG),                       # query heads not a multiple of kv heads
+    (dict(dq=None), _lib.E_BAD_ARG),
+    (dict(scale=0.0), _lib.E_BAD_ARG),
+    (dict(E=136), _lib.E_UNSUPPORTED),                   # backward kernels: head dims up to 128
+    (dict(dk=FAKE + 8), _lib.E_MISALIGNED),
+    (dict(q_stride=(8 * 300 * 128, 300 * 128, 132)), _lib.E_MISALIGNED),
+    (dict(dv_stride=(2 * 300 * 128, 300 * 128, 64)), _lib.E_BAD_ARG),   # rows overlap
+    (dict(lse_stride=(8 * 300, 100)), _lib.E_BAD_ARG),
+    (dict(workspace_bytes=1024), _lib.E_WORKSPACE),
+    (dict(workspace=FAKE + 64), _lib.E_MISALIGNED),
+])
+def test_backward_rejects_bad_problems_before_touching_the_device(lib, over, code):
+    """Validation runs first and on the host: these calls return before any CUDA call."""
+    lib.flb200_attn_bwd.restype = C.c_int
+    assert lib.flb200_attn_bwd(C.byref(good_bwd(**over)), None) == code
