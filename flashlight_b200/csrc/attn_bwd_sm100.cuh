@@ -242,14 +242,6 @@ FLB_DEV void bwd_exit(const BwdSmem<C>& sm, const BwdParams& p, int warp) {
 // ------------------------------------------------------------------------------------------
 // delta[n][h][i] = sum_d dO * O   (rows beyond L of the padded array: 0)
 // ------------------------------------------------------------------------------------------
-// hi + lo = v to about 16 bits; a non-finite v gives (-inf, 0): the exponential of such a row's scores is 0
-FLB_DEV uint32_t bwd_split_bf16(float v) {
-  if (!(fabsf(v) <= 3.0e38f)) return 0xFF80u;
-  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-  const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-  return static_cast<uint32_t>(__bfloat16_as_ushort(hi)) | (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
-}
-
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                       int64_t o_sn, int64_t o_sh, int64_t o_sl, int64_t do_sn, int64_t do_sh,
                                       int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta,
@@ -285,11 +277,11 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const
   const uint4 zero = make_uint4(0, 0, 0, 0);
   if (sub == 0) {
     delta[row] = acc;
-    yrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? bwd_split_bf16(-acc) : 0u, 0, 0, 0);
+    yrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(-acc) : 0u, 0, 0, 0);
     yrows[2 * static_cast<int64_t>(row) + 1] = zero;
   } else if (sub == 1) {
     const float x = i < L ? -lse[n * lse_sn + h * lse_sh + i] * inv_scale : 0.f;
-    xrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? bwd_split_bf16(x) : 0u, 0, 0, 0);
+    xrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(x) : 0u, 0, 0, 0);
     xrows[2 * static_cast<int64_t>(row) + 1] = zero;
   }
 }

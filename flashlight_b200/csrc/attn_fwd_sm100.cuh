@@ -213,6 +213,9 @@ struct Smem {
     return base + C::STAGES * C::Q_BYTES + C::OSTAGE_BYTES + (s * slots + i) * C::K_HEAD_BYTES;
   }
   FLB_DEV uint8_t* bias(int slots) const { return ring(2, 0, slots); }
+  // behind the `nt` bias tiles, when the tensor cores add the key vector: 4 KB tiles of 128 rows of 16
+  // bf16 (32-byte swizzle); tile 0 holds ones, then slots / 2 tiles per stage that travel with the K tiles
+  FLB_DEV uint8_t* kvx(int slots, int nt, int i) const { return bias(slots) + nt * 32768 + i * 4096; }
   FLB_DEV uint8_t* aux() const { return base + (C::SMEM_USED - 1024 - C::AUX_BYTES); }
   FLB_DEV uint32_t bar(int id) const { return smem_u32(aux()) + id * 8; }
   FLB_DEV uint32_t* tmem_base() const { return reinterpret_cast<uint32_t*>(aux() + 384); }
@@ -346,12 +349,16 @@ FLB_DEV void load_role_rows(const Smem<C>& sm, const CUtensorMap* tmQ, const CUt
       for (int kv = 0; kv < 2; ++kv) {  // K(t), then V(t)
         FLB_WAIT(sm, BAR_RING_EMPTY + 8 * s + slot, ph ^ 1);
         const uint32_t full = sm.bar(BAR_RING_FULL + 8 * s + slot);
-        mbar_arrive_expect_tx(full, C::K_HEAD_BYTES);
+        const bool with_x = kv == 0 && p.keyvec_rows != nullptr;   // the K tile's key-vector rows travel with it
+        mbar_arrive_expect_tx(full, C::K_HEAD_BYTES + (with_x ? 4096 : 0));
         const uint32_t dst = smem_u32(sm.ring(s, slot, p.res_slots));
         if (kv == 0) {
 #pragma unroll
           for (int kb = 0; kb < C::NKB; ++kb)
             tma_load_4d(dst + kb * C::QK_BOX_BYTES, tmK, full, kb * C::KBOX, t * kTileN, h, n);
+          if (with_x)
+            bulk_load_1d(smem_u32(sm.kvx(p.res_slots, rw.nt, 1 + s * (p.res_slots >> 1) + (slot >> 1))),
+                         p.keyvec_rows + (static_cast<int64_t>(n) * p.keyvec_tiles + t) * 4096, 4096, full);
         } else {
 #pragma unroll
           for (int vb = 0; vb < C::NVB; ++vb)
@@ -386,6 +393,11 @@ FLB_DEV void mma_role_rows(const Smem<C>& sm, uint32_t tmem, const KernelParams&
   constexpr uint32_t v_hi = static_cast<uint32_t>(vdesc0 >> 32), v_lo0 = static_cast<uint32_t>(vdesc0);
   const uint32_t q_lo = k_lo0 + ((smem_u32(sm.q(s)) & 0x3FFFFu) >> 4);
   const uint32_t ring0 = (smem_u32(sm.ring(s, 0, p.res_slots)) & 0x3FFFFu) >> 4;
+  // K-major tiles of 32-byte swizzled rows (the key-vector k-step)
+  constexpr uint64_t xdesc0 = (static_cast<uint64_t>(256 >> 4) << 32) | (1ull << 16) | (1ull << 46) |
+                              (static_cast<uint64_t>(kSwz32) << 61);
+  constexpr uint32_t x_hi = static_cast<uint32_t>(xdesc0 >> 32), x_lo0 = static_cast<uint32_t>(xdesc0);
+  const uint32_t kvx0 = (smem_u32(sm.kvx(p.res_slots, rw.nt, 0)) & 0x3FFFFu) >> 4;
   const int total = rw.items(s) * rw.nt;
   // ring slots in load order K(0) V(0) K(1) V(1) ...: K(u) is load 2u, V(u-1) load 2u - 1
   int kslot = 0, vslot = p.res_slots > 1 ? p.res_slots - 1 : 0;  // load -1 precedes load 0
@@ -413,6 +425,11 @@ FLB_DEV void mma_role_rows(const Smem<C>& sm, uint32_t tmem, const KernelParams&
         const int kk = k * 16;
         const uint32_t off = ((kk / C::KBOX) * C::QK_BOX_BYTES + (kk % C::KBOX) * 2) >> 4;
         umma_ss_c<1>(leader, tS, q_lo + off, k_lo + off, k_hi, idesc_qk);
+      }
+      if (p.keyvec_rows != nullptr) {
+        // one more k-step of 16: ones x [hi, lo, 0 ...] adds bias / scale of each key to its score column
+        const uint32_t x_lo = x_lo0 + kvx0 + (1 + s * (p.res_slots >> 1) + (kslot >> 1)) * (4096 >> 4);
+        umma_ss_c<1>(leader, tS, x_lo0 + kvx0, x_lo, x_hi, idesc_qk);
       }
       umma_commit_c(leader, sm.bar(BAR_S_FULL + s));
       umma_commit_c(leader, sm.bar(BAR_RING_EMPTY + 8 * s + kslot));
@@ -762,7 +779,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
           v[c8 * 8 + 2 * e + 1] = f2u(x.y);
         }
       }
-      if (brow[0]) {
+      if (brow[0] && p.keyvec_rows == nullptr) {
         if (j0 + kTileN <= p.S && p.bias_vec[0]) {
           const uint4* src = reinterpret_cast<const uint4*>(brow[0] + j0);  // same address in every lane
 #pragma unroll
@@ -1353,6 +1370,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     rg[1] = TileRange{0, rw.items(1) * rw.nt};
     lo = 0;
     hi = rg[0].hi;
+    // A operand of the key-vector k-step: rows [1, 1, 0 x 6 | 1, 1, 0 x 6] (both 16-byte chunks alike,
+    // so the 32-byte swizzle leaves the tile as written); the set-up barriers below publish it
+    if (p.keyvec_rows != nullptr && threadIdx.x < 128) {
+      uint4* r = reinterpret_cast<uint4*>(sm.kvx(p.res_slots, rw.nt, 0) + threadIdx.x * 32);
+      r[0] = make_uint4(0x3F803F80u, 0, 0, 0);
+      r[1] = make_uint4(0x3F803F80u, 0, 0, 0);
+      fence_proxy_async_smem();
+    }
   }
 
   // the warps that issue loads (the resident-bias kernel has one per stage, and one MMA warp per stage:

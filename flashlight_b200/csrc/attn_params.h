@@ -63,6 +63,11 @@ struct KernelParams {
   int pair_h, pair_b;
   int res_rows, res_chunks;
   int res_slots;  // slots (one tile each) of each stage's K/V ring; the bias tiles lie behind the rings
+  // resident-bias kernel with the key vector added by the tensor cores: per (row, key) a 16-column
+  // bf16 row [hi, lo, 0 ...] of bias / scale, written by keyvec_rows_kernel in the shared-memory image
+  // of a 32-byte swizzled tile (4 KB per 128 keys); nullptr: the softmax threads add the vector
+  const uint8_t* keyvec_rows;
+  int keyvec_tiles;  // key tiles per row (row stride = keyvec_tiles * 4096 bytes)
   // masks
   int causal;                // document mask: also require j <= i
   int window;                // sliding window (keys i-window .. i)

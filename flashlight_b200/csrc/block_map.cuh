@@ -7,6 +7,7 @@
 // diagonal band of full tiles).  Everything else is masked element-wise by the attention kernel.
 #pragma once
 #include "attn_params.h"
+#include "ptx.cuh"
 
 namespace flb {
 
@@ -111,6 +112,22 @@ doc_runs_kernel(const long long* __restrict__ doc, long long doc_sn, int L,
   int32_t* e = map_runs + (static_cast<long long>(n) * L + i) * 2;
   e[0] = a;
   e[1] = c;
+}
+
+// Key-vector rows for the resident-bias kernel: out holds, per (row n, key tile t), the 4 KB shared-memory
+// image of a tile of 128 rows of 16 bf16 with 32-byte swizzle (the 16-byte chunk index of row r is
+// XORed with bit 2 of r), row j = [hi, lo, 0 ...] of bias[n][j] / scale; keys beyond S: zeros.
+__global__ void keyvec_rows_kernel(const __nv_bfloat16* __restrict__ bias, int64_t sb, int64_t sr, int R, int S,
+                                   int Sp, int64_t total, float inv_scale, uint4* __restrict__ out) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int j = static_cast<int>(idx % Sp);
+  const int64_t n = idx / Sp;
+  const int64_t b = n / R, r = n % R;
+  const uint32_t word = j < S ? split_bf16_pair(__bfloat162float(bias[b * sb + r * sr + j]) * inv_scale) : 0u;
+  const int swap = ((j & 127) >> 2) & 1;
+  out[2 * idx + swap] = make_uint4(word, 0, 0, 0);
+  out[2 * idx + (swap ^ 1)] = make_uint4(0, 0, 0, 0);
 }
 
 }  // namespace flb

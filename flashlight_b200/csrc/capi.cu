@@ -246,6 +246,10 @@ struct ResidentPlan {
   int pair = -1, rowvec = -1;  // indices into p->bias
   int rows = 0, chunks = 0;    // rows per CTA, CTAs per (batch element, head, query tile)
   int slots = 0;               // K/V ring slots that fit beside the bias tiles
+  // the key vector added by the tensor cores (one more k-step per score product): bytes of the rows the
+  // pre-kernel writes into the caller's workspace (0: not eligible), and whether this call does it
+  size_t keyvec_bytes = 0;
+  bool keyvec = false;
 };
 
 ResidentPlan plan_resident(const flb200_attn_params* p, int width) {
@@ -289,6 +293,23 @@ ResidentPlan plan_resident(const flb200_attn_params* p, int width) {
   r.rows = rows;
   r.chunks = (R + rows - 1) / rows;
   r.use = true;
+  // Key vector through the tensor cores: one vector per row (no head axis), and an even number of at least
+  // four ring slots per stage beside the tile of ones and the slots / 2 tiles of rows per stage that
+  // travel with the K tiles (4 KB each).  It needs scratch memory from the caller; without it the
+  // softmax threads add the vector as before.
+  if (r.rowvec >= 0 && p->bias_stride[r.rowvec][2] == 0) {
+    int even = std::min(6, r.slots) & ~1;
+    while (even >= 4 && 2 * even * tile_bytes + 4096 * (1 + even) > room) even -= 2;
+    bool on = even >= 4;
+    if (const char* e = std::getenv("FLB200_KEYVEC_MMA")) on = on && std::atoi(e) != 0;
+    if (on) {
+      r.keyvec_bytes = static_cast<size_t>(p->N) * nt * 4096;
+      if (p->workspace && p->workspace_bytes >= r.keyvec_bytes && aligned16(p->workspace)) {
+        r.keyvec = true;
+        r.slots = even;
+      }
+    }
+  }
   return r;
 }
 
@@ -388,7 +409,13 @@ int flb200_attn_validate(const flb200_attn_params* p) { return validate(p); }
 
 size_t flb200_attn_workspace_bytes(const flb200_attn_params* p) {
   if (!p || p->struct_size != sizeof(flb200_attn_params)) return 0;
-  if (p->mask != FLB200_MASK_DOCUMENT || p->N <= 0 || p->L <= 0 || p->S <= 0) return 0;
+  if (p->N <= 0 || p->L <= 0 || p->S <= 0) return 0;
+  if (p->score_mod == FLB200_SCORE_BIAS && p->mask == FLB200_MASK_NONE && validate(p) == FLB200_OK) {
+    // optional scratch of the resident pair-bias kernel (the call also runs without it)
+    const int width = kernel_width(p->E, p->Ev, kernel_score(p), p->mask, p->diff);
+    return width ? plan_resident(p, width).keyvec_bytes : 0;
+  }
+  if (p->mask != FLB200_MASK_DOCUMENT) return 0;
   return map_layout(p).total;
 }
 
@@ -521,6 +548,17 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
     kp.bias_vec[0] = rv >= 0 && aligned16(p->bias[rv]) && mult8(p->bias_stride[rv][0]) &&
                      mult8(p->bias_stride[rv][1]) && mult8(p->bias_stride[rv][2]);
     kp.bias[1] = nullptr;
+    if (res.keyvec) {
+      const int nt = (p->S + kTileN - 1) / kTileN;
+      const int64_t total = static_cast<int64_t>(p->N) * nt * kTileN;
+      kp.keyvec_rows = static_cast<const uint8_t*>(p->workspace);
+      kp.keyvec_tiles = nt;
+      keyvec_rows_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(p->bias[rv]), p->bias_stride[rv][0], p->bias_stride[rv][1], R, p->S,
+          nt * kTileN, total, 1.0f / p->scale, reinterpret_cast<uint4*>(p->workspace));
+      if (cudaGetLastError() != cudaSuccess) return FLB200_E_LAUNCH;
+      flb::count_launches(1);
+    }
     // pair bias as (key, query, head, batch element); broadcast axes get extent 1
     const uint64_t dh = kp.pair_h ? p->Hq : 1, db = kp.pair_b ? B : 1;
     const uint64_t sh = kp.pair_h ? st[2] : ((static_cast<uint64_t>(st[3]) * p->L + 7) & ~7ull);

@@ -170,6 +170,14 @@ FLB_DEV void tma_prefetch_desc(const void* tmap) {
 
 // 4-D tiled load global -> this CTA's shared memory; completion on `bar`.
 // c0 is the innermost coordinate and must keep c0 * elem_size a multiple of 16.
+// untiled bulk copy global -> this CTA's shared memory (16-byte aligned addresses, size a multiple of
+// 16 bytes), completion counted on an mbarrier like a tensor-map load
+FLB_DEV void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 FLB_DEV void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1, int c2,
                          int c3) {
   asm volatile(
@@ -461,6 +469,15 @@ FLB_DEV uint32_t pack_bf16(float lo, float hi) {
   uint32_t y;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
   return y;
+}
+
+// hi + lo = v to about 16 bits, packed {lo half: hi term, hi half: lo term}; a non-finite v gives
+// (-inf, 0): a score it is added to becomes -inf, its exponential 0
+FLB_DEV uint32_t split_bf16_pair(float v) {
+  if (!(fabsf(v) <= 3.0e38f)) return 0xFF80u;
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  const __nv_bfloat16 lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+  return static_cast<uint32_t>(__bfloat16_as_ushort(hi)) | (static_cast<uint32_t>(__bfloat16_as_ushort(lo)) << 16);
 }
 
 // 2^x for a pair of non-positive-ish arguments on the FMA pipe, to take load off the

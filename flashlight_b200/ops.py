@@ -242,6 +242,14 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap,
             ws.record_stream(cur)
             keep.append(ws)
             p.workspace, p.workspace_bytes, p.block_map_ready = ws.data_ptr(), ws.numel(), 1
+        elif score_mod == _lib.SCORE_BIAS:
+            # optional scratch of the resident pair-bias kernel (its key-vector rows); stream-ordered
+            # like every other temporary of this call
+            nbytes = lib.flb200_attn_workspace_bytes(C.byref(p))
+            if nbytes:
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+                keep.append(ws)
+                p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         rc = lib.flb200_attn_fwd(C.byref(p), C.c_void_p(stream))
     if rc != _lib.OK:
         _raise_for(rc, "attn_fwd")

@@ -136,7 +136,11 @@ typedef struct flb200_attn_params {
   /* DOCUMENT needs flb200_attn_workspace_bytes() bytes of device scratch for the
    * block map.  With block_map_ready == 0, flb200_attn_fwd builds the map on the
    * same stream first; a caller that reuses document_id across calls builds it
-   * once with flb200_build_block_map and passes block_map_ready = 1. */
+   * once with flb200_build_block_map and passes block_map_ready = 1.
+   * SCORE_BIAS: optional.  When one bias is a pair bias shared by bias_inner >= 4 rows and the other a
+   * key vector per row, heads are narrow and flb200_attn_workspace_bytes() bytes (16-byte aligned) are
+   * given, a small kernel lays the key vector out there and the tensor cores add it to the scores;
+   * with workspace == NULL the same result comes from the softmax threads, more slowly. */
   void* workspace;
   size_t workspace_bytes;
   int32_t block_map_ready;
@@ -191,8 +195,8 @@ const char* flb200_strerror(int status);
 /* Host-only check of a problem description: no CUDA call is made. */
 int flb200_attn_validate(const flb200_attn_params* p);
 
-/* Device scratch bytes flb200_attn_fwd needs for `p` (0 unless mask == DOCUMENT).
- * Returns 0 for a NULL or invalid description. */
+/* Device scratch bytes flb200_attn_fwd takes for `p`: required for mask == DOCUMENT, optional for
+ * SCORE_BIAS (see `workspace`), 0 otherwise.  Returns 0 for a NULL or invalid description. */
 size_t flb200_attn_workspace_bytes(const flb200_attn_params* p);
 
 /* Build the document-mask block map into p->workspace on `cuda_stream`. */
@@ -248,8 +252,8 @@ int flb200_selftest_wait_timeout(const flb200_attn_params* p, void* cuda_stream)
  * All tensors bf16 with the layouts and stride conventions of the forward's parameter block: q, o,
  * dout, dq are [N][Hq][L][E]; k, v, dk, dv are [N][Hkv][S][E]; head dims up to 128, the same for q/k
  * and v.
- * `workspace`: flb200_attn_bwd_workspace_bytes() bytes of device scratch (fp32 row sums), 256-byte
- * aligned.  Three launches on `cuda_stream`.
+ * `workspace`: flb200_attn_bwd_workspace_bytes() bytes of device scratch (per query row the fp32 row
+ * sum and two 32-byte rows for the dK/dV kernel), 256-byte aligned.  Three launches on `cuda_stream`.
  */
 typedef struct flb200_attn_bwd_params {
   uint32_t struct_size;

@@ -233,6 +233,28 @@ def test_evoformer(D, S, stages):
     check(av.attention_reference(q, k, v, []), ao.evoformer(q, k, v, []))
 
 
+def test_evoformer_key_vector_added_by_the_tensor_cores(monkeypatch):
+    """Resident pair-bias kernel (four or more rows share a pair bias, narrow heads): the per-row key
+    vector, with its -inf entries, is added by one more k-step of the score product when the caller gives
+    scratch memory (one launch more: the kernel that lays the vector out), by the softmax threads otherwise."""
+    B, N, H, S, D = 2, 6, 4, 328, 32   # rows of the pair bias start on 16-byte boundaries (TMA)
+    q, k, v = rnd((B, N, S, H, D), 60), rnd((B, N, S, H, D), 61), rnd((B, N, S, H, D), 62)
+    pair = rnd((B, 1, H, S, S), 63)
+    g = torch.Generator().manual_seed(64)
+    keep = torch.rand(B, N, 1, 1, S, generator=g) < 0.8
+    keep[..., 5] = True
+    vec = (torch.randn(B, N, 1, 1, S, generator=g) * 3).masked_fill(~keep, float("-inf")).to(torch.bfloat16).cuda()
+    ref = ao.evoformer(q, k, v, [vec, pair])
+    outs = {}
+    for flag, launches in (("1", 2), ("0", 1)):
+        monkeypatch.setenv("FLB200_KEYVEC_MMA", flag)
+        n0 = flashlight_b200.launch_count()
+        outs[flag] = av.attention_reference(q, k, v, [vec, pair])
+        assert flashlight_b200.launch_count() - n0 == launches
+        check(outs[flag], ref, flag)
+    assert (outs["1"].float() - outs["0"].float()).abs().max().item() <= 2e-2
+
+
 # ---------------------------------------------------------------- the reference tests' own inputs
 def close_ref(out, ref):
     """assert_close(atol=2e-2, rtol=1e-2) as in the reference's tests (tests/test_vanilla.py:36).
