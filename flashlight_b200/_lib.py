@@ -98,6 +98,21 @@ class AttnBwdParams(C.Structure):
     ]
 
 
+class IpaPackParams(C.Structure):
+    """Mirror of `flb200_ipa_pack_params`."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("rows_q", C.c_int32), ("rows_k", C.c_int32),
+        ("C", C.c_int32), ("P_qk", C.c_int32), ("P_v", C.c_int32), ("point_dim", C.c_int32),
+        ("q_scalar", C.c_void_p), ("k_scalar", C.c_void_p), ("v_scalar", C.c_void_p),
+        ("q_points", C.c_void_p), ("k_points", C.c_void_p), ("v_points", C.c_void_p),
+        ("a", C.c_float),
+        ("E", C.c_int32), ("Ev", C.c_int32),
+        ("q_aug", C.c_void_p), ("k_aug", C.c_void_p), ("v_aug", C.c_void_p),
+    ]
+
+
 EXPORTS = (
     "flb200_abi_version",
     "flb200_strerror",
@@ -109,6 +124,7 @@ EXPORTS = (
     "flb200_selftest_wait_timeout",
     "flb200_attn_bwd_workspace_bytes",
     "flb200_attn_bwd",
+    "flb200_ipa_pack",
     "flb200_decode_status",
     "flb200_launch_count",
 )
@@ -148,6 +164,8 @@ def load() -> C.CDLL:
     lib.flb200_attn_bwd_workspace_bytes.argtypes = [PB]
     lib.flb200_attn_bwd.restype = C.c_int
     lib.flb200_attn_bwd.argtypes = [PB, C.c_void_p]
+    lib.flb200_ipa_pack.restype = C.c_int
+    lib.flb200_ipa_pack.argtypes = [C.POINTER(IpaPackParams), C.c_void_p]
     lib.flb200_decode_status.restype = C.c_int
     lib.flb200_decode_status.argtypes = [C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.flb200_launch_count.restype = C.c_uint64

@@ -5,16 +5,8 @@ from typing import Optional, Tuple
 import torch
 
 from .. import _lib
+from ..ops import ipa_pack
 from ._dispatch import run
-
-
-def _split_bf16(t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    hi = t.to(torch.bfloat16)
-    return hi, (t - hi.float()).to(torch.bfloat16)
-
-
-def _pad_to(t: torch.Tensor, width: int) -> torch.Tensor:
-    return t if t.size(-1) == width else torch.nn.functional.pad(t, (0, width - t.size(-1)))
 
 
 def invariant_point_attention(
@@ -33,7 +25,8 @@ def invariant_point_attention(
     """softmax(q.k / sqrt(c_hidden) + w * sum_p |q_p - k_p|^2 + pair_bias) applied to the scalar and the
     point values, w = -0.5 sqrt(9 / (2 no_qk_points)) (tests/test_ipa.py:83-124).
 
-    One launch of the pair-bias kernel.  With a = w sqrt(c_hidden) the logits are
+    One launch of the pair-bias kernel behind one that assembles its operands (`flb200_ipa_pack`).  With
+    a = w sqrt(c_hidden) the logits are
     (q.k + a |k_p|^2 - 2 a q_p.k_p) / sqrt(c_hidden) + bias + a row constant (w |q_p|^2, which the
     softmax cancels), so the squared distances become extra columns of the q/k operands:
 
@@ -56,24 +49,17 @@ def invariant_point_attention(
     dt = torch.bfloat16
     if any(t.dtype != dt for t in (q_scalar, k_scalar, v_scalar, q_points, k_points, v_points, pair_bias)):
         raise NotImplementedError("invariant_point_attention: bfloat16 inputs only")
+    if not q_scalar.is_cuda:
+        raise NotImplementedError("invariant_point_attention: CUDA tensors only")
     scale = 1.0 / (c_hidden ** 0.5)
     a = -0.5 * (9.0 / (2 * no_qk_points)) ** 0.5 / scale
-    qp = q_points.reshape(B, H, N, -1)
-    kp = k_points.reshape(B, H, Nk, -1).float()
-    t_hi, t_lo = _split_bf16(kp * (-2.0 * a))
-    n_hi, n_lo = _split_bf16((kp * kp).sum(dim=-1, keepdim=True) * a)
-    one = torch.ones(B, H, N, 2, dtype=dt, device=q_scalar.device)
-    q_aug = torch.cat([q_scalar, qp, qp, one], dim=-1)
-    k_aug = torch.cat([k_scalar, t_hi, t_lo, n_hi, n_lo], dim=-1)
-    v_aug = torch.cat([v_scalar, v_points.reshape(B, H, Nk, -1)], dim=-1)
-    E = -(-q_aug.size(-1) // 8) * 8  # rows start on 16-byte boundaries
-    Ev_real = v_aug.size(-1)
-    Ev = -(-Ev_real // 8) * 8
-    if max(E, Ev) > 128:
+    q_aug, k_aug, v_aug = ipa_pack(q_scalar, k_scalar, v_scalar, q_points, k_points, v_points, a)
+    Ev_real = C + v_points.size(-2) * v_points.size(-1)
+    if max(q_aug.size(-1), v_aug.size(-1)) > 128:
         raise NotImplementedError("invariant_point_attention: operand width above 128 columns")
     bias = pair_bias if pair_bias.stride(-1) == 1 else pair_bias.contiguous()
-    out = run(_pad_to(q_aug, E), _pad_to(k_aug, E), _pad_to(v_aug, Ev), scale=scale,
-              score_mod=_lib.SCORE_BIAS, biases=[bias.unsqueeze(1), None], bias_inner=1)
+    out = run(q_aug, k_aug, v_aug, scale=scale, score_mod=_lib.SCORE_BIAS, biases=[bias.unsqueeze(1), None],
+              bias_inner=1)
     out_scalar = out[..., :C]
     out_points = out[..., C:Ev_real].reshape(B, H, N, v_points.size(-2), v_points.size(-1)).transpose(1, 2)
     return out_scalar, out_points

@@ -337,6 +337,35 @@ def attention_with_grad(q, k, v, scale: float, causal: bool) -> torch.Tensor:
 _POINTWISE = {"identity": _lib.PW_IDENTITY, "relu": _lib.PW_RELU, "tanh": _lib.PW_TANH, "sigmoid": _lib.PW_SIGMOID}
 
 
+def ipa_pack(q_scalar, k_scalar, v_scalar, q_points, k_points, v_points, a: float):
+    """Augmented operands of invariant point attention (`flb200_ipa_pack`): returns q', k' `[B, H, N, E]` and
+    v' `[B, H, N_k, Ev]` for a pair-biased forward with scale 1 / sqrt(c_hidden)."""
+    lib = _lib.load()
+    B, H, N, Cw = q_scalar.shape
+    Nk = k_scalar.size(2)
+    P_qk, pd = q_points.shape[-2:]
+    P_v = v_points.size(-2)
+    E = -(-(Cw + 2 * P_qk * pd + 2) // 8) * 8
+    Ev = -(-(Cw + P_v * pd) // 8) * 8
+    ts = [t.contiguous() for t in (q_scalar, k_scalar, v_scalar, q_points, k_points, v_points)]
+    dev, dt = q_scalar.device, torch.bfloat16
+    qa = torch.empty(B, H, N, E, dtype=dt, device=dev)
+    ka = torch.empty(B, H, Nk, E, dtype=dt, device=dev)
+    va = torch.empty(B, H, Nk, Ev, dtype=dt, device=dev)
+    p = _lib.IpaPackParams()
+    p.struct_size = C.sizeof(_lib.IpaPackParams)
+    p.rows_q, p.rows_k = B * H * N, B * H * Nk
+    p.C, p.P_qk, p.P_v, p.point_dim = Cw, P_qk, P_v, pd
+    (p.q_scalar, p.k_scalar, p.v_scalar, p.q_points, p.k_points, p.v_points) = (t.data_ptr() for t in ts)
+    p.a, p.E, p.Ev = float(a), E, Ev
+    p.q_aug, p.k_aug, p.v_aug = qa.data_ptr(), ka.data_ptr(), va.data_ptr()
+    with torch.cuda.device(dev):
+        rc = lib.flb200_ipa_pack(C.byref(p), C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    if rc != _lib.OK:
+        _raise_for(rc, "ipa_pack")
+    return qa, ka, va
+
+
 @torch.library.custom_op("flb200::product_chain", mutates_args=())
 def product_chain(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, scale: float, pointwise: str) -> torch.Tensor:
     """f((a @ b) * scale) @ c in one kernel, no softmax: a [B, M, N], b [B, N, O], c [B, O, P] bf16 with

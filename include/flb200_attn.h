@@ -288,6 +288,34 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream);
  * block that gave up first. */
 int flb200_decode_status(int32_t status_word, int32_t* barrier, int32_t* block);
 
+/* Operands of invariant point attention for flb200_attn_fwd (the reference states the operator in
+ * tests/test_ipa.py:57-125; it has no kernel or binding of its own).  The logits
+ *   q.k / sqrt(c_hidden) + w sum_p |q_p - k_p|^2 + pair_bias
+ * equal, up to a term constant along each row, (q'.k') / sqrt(c_hidden) + pair_bias with
+ *   q' = [ q | q_p | q_p | 1 | 1 | 0.. ],  k' = [ k | hi(-2a k_p) | lo(-2a k_p) | hi(a |k_p|^2) | lo(a |k_p|^2) | 0.. ],
+ * a = w sqrt(c_hidden), hi + lo the two-term bf16 split of an fp32 value, and the values are v' = [ v | v_p | 0.. ].
+ * One launch writes the three operands; the caller then runs flb200_attn_fwd on them with
+ * score_mod = BIAS, bias[0] = pair_bias and scale = 1 / sqrt(c_hidden).
+ * All inputs bf16 and dense: scalars [rows][C], points [rows][P][point_dim]; outputs [rows][E] / [rows_k][Ev]
+ * with E >= C + 2 P_qk point_dim + 2 and Ev >= C + P_v point_dim, both multiples of 8. */
+typedef struct flb200_ipa_pack_params {
+  uint32_t struct_size;
+  int32_t rows_q, rows_k;       /* B * H * N query rows; B * H * N_k key / value rows */
+  int32_t C, P_qk, P_v, point_dim;
+  const void* q_scalar;
+  const void* k_scalar;
+  const void* v_scalar;
+  const void* q_points;
+  const void* k_points;
+  const void* v_points;
+  float a;                      /* w * sqrt(c_hidden), w = -0.5 sqrt(9 / (2 P_qk)) in the reference */
+  int32_t E, Ev;                /* row widths of the outputs */
+  void* q_aug;
+  void* k_aug;
+  void* v_aug;
+} flb200_ipa_pack_params;
+int flb200_ipa_pack(const flb200_ipa_pack_params* p, void* cuda_stream);
+
 /* Number of kernels this library has launched since it was loaded (attention
  * and block-map kernels; for accounting in benchmarks). */
 uint64_t flb200_launch_count(void);

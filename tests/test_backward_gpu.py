@@ -95,3 +95,28 @@ def test_backward_is_deterministic():
     for _ in range(3):
         again = grads(fn, q, k, v, dout)
         assert all(torch.equal(x, y) for x, y in zip(first, again))
+
+
+def test_backward_long_causal_sequence_with_groups_of_four():
+    """Sixteen key tiles per query head and four query heads per kv head: the rings of both kernels wrap
+    several times and the dK/dV kernel walks 4 x 16 steps."""
+    q, k, v, dout = rnd((1, 8, 2048, 128), 14), rnd((1, 2, 2048, 128), 15), rnd((1, 2, 2048, 128), 16), rnd((1, 8, 2048, 128), 17)
+    fn = lambda a, b, c: av.attention_pytorch_causal(a, b, c, enable_gqa=True)
+    fo = lambda a, b, c: ao.causal(a, b, c, enable_gqa=True)
+    _, dq, dk, dv = grads(fn, q, k, v, dout)
+    _, rq, rk, rv = grads(fo, q.float(), k.float(), v.float(), dout.float())
+    close(dq, rq, "dq")
+    close(dk, rk, "dk")
+    close(dv, rv, "dv")
+
+
+def test_backward_of_strided_views():
+    """q, k, v as [N, L, H, D] storage seen as [N, H, L, D]: the tensor maps carry the strides."""
+    base = [rnd((2, 300, 4, 64), 18 + i) for i in range(3)]
+    q, k, v = (t.transpose(1, 2) for t in base)
+    dout = rnd((2, 4, 300, 64), 21)
+    _, dq, dk, dv = grads(lambda a, b, c: av.attention_pytorch_causal(a, b, c), q, k, v, dout)
+    _, rq, rk, rv = grads(lambda a, b, c: ao.causal(a, b, c), q.float(), k.float(), v.float(), dout.float())
+    close(dq, rq, "dq")
+    close(dk, rk, "dk")
+    close(dv, rv, "dv")

@@ -218,3 +218,20 @@ def test_backward_rejects_bad_problems_before_touching_the_device(lib, over, cod
     """Validation runs first and on the host: these calls return before any CUDA call."""
     lib.flb200_attn_bwd.restype = C.c_int
     assert lib.flb200_attn_bwd(C.byref(good_bwd(**over)), None) == code
+
+
+def test_ipa_pack_rejects_bad_descriptions_on_the_host(lib):
+    p = _lib.IpaPackParams()
+    p.struct_size = C.sizeof(_lib.IpaPackParams)
+    p.rows_q = p.rows_k = 64
+    p.C, p.P_qk, p.P_v, p.point_dim = 16, 4, 8, 4
+    for name in ("q_scalar", "k_scalar", "v_scalar", "q_points", "k_points", "v_points", "q_aug", "k_aug", "v_aug"):
+        setattr(p, name, FAKE)
+    p.a, p.E, p.Ev = -2.1, 48, 48          # E must hold 16 + 2 * 16 + 2 = 50 columns
+    assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
+    p.E, p.Ev = 56, 44                     # widths are multiples of 8
+    assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
+    p.Ev, p.k_points = 48, None
+    assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
+    p.k_points, p.struct_size = FAKE, 12
+    assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
