@@ -124,6 +124,7 @@ EXPORTS = (
     "flb200_selftest_wait_timeout",
     "flb200_attn_bwd_workspace_bytes",
     "flb200_attn_bwd",
+    "flb200_selftest_bwd_wait_timeout",
     "flb200_ipa_pack",
     "flb200_decode_status",
     "flb200_launch_count",
@@ -164,6 +165,8 @@ def load() -> C.CDLL:
     lib.flb200_attn_bwd_workspace_bytes.argtypes = [PB]
     lib.flb200_attn_bwd.restype = C.c_int
     lib.flb200_attn_bwd.argtypes = [PB, C.c_void_p]
+    lib.flb200_selftest_bwd_wait_timeout.restype = C.c_int
+    lib.flb200_selftest_bwd_wait_timeout.argtypes = [PB, C.c_void_p]
     lib.flb200_ipa_pack.restype = C.c_int
     lib.flb200_ipa_pack.argtypes = [C.POINTER(IpaPackParams), C.c_void_p]
     lib.flb200_decode_status.restype = C.c_int

@@ -76,7 +76,25 @@ size_t flb200_attn_bwd_workspace_bytes(const flb200_attn_bwd_params* p) {
   return static_cast<size_t>(p->N) * p->Hq * lp * (sizeof(float) + 2 * 32);
 }
 
+namespace {
+int attn_bwd_impl(const flb200_attn_bwd_params* p, void* cuda_stream, bool withhold_loads);
+}
+
 int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
+  return attn_bwd_impl(p, cuda_stream, false);
+}
+
+int flb200_selftest_bwd_wait_timeout(const flb200_attn_bwd_params* p, void* cuda_stream) {
+  if (!p || p->struct_size != sizeof(flb200_attn_bwd_params) || !p->status) return FLB200_E_BAD_ARG;
+  flb200_attn_bwd_params q = *p;
+  if (q.wait_limit_us == 0) q.wait_limit_us = 1000;
+  return attn_bwd_impl(&q, cuda_stream, true);
+}
+
+}  // extern "C"
+
+namespace {
+int attn_bwd_impl(const flb200_attn_bwd_params* p, void* cuda_stream, bool withhold_loads) {
   const int v = validate_bwd(p);
   if (v != FLB200_OK) return v;
   // (cudaSetDevice binds the device's primary context to this thread: the tensor-map encoder is a
@@ -108,6 +126,7 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
   bp.status = p->status;
   bp.status_host = p->status_host;
   bp.wait_limit_us = p->wait_limit_us ? p->wait_limit_us : kDefaultWaitLimitUs;
+  bp.withhold_loads = withhold_loads ? 1 : 0;
 
   // head dims below a built width run on it: the tensor maps zero-fill the missing feature columns
   const int width = p->E <= 64 ? 64 : 128;
@@ -146,4 +165,4 @@ int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream) {
   return FLB200_OK;
 }
 
-}  // extern "C"
+}  // namespace

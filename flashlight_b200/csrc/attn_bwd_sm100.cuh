@@ -51,6 +51,7 @@ struct BwdParams {
   int* status;
   int* status_host;
   uint32_t wait_limit_us;
+  int withhold_loads;  // wait self-test: the producers load nothing, every role's first wait runs out
 };
 
 enum : int {
@@ -419,6 +420,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   };
   auto produce = [&]() {
+    if (p.withhold_loads) return;
     if (nk > 0) {
       mbar_arrive_expect_tx(sm.bar(BB_RES_FULL), 2 * C::TILE_BYTES);
       bwd_load_tile<C>(sm.res(0), &tmQ, sm.bar(BB_RES_FULL), i0, h, n);
@@ -629,6 +631,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tma_load_4d(smem_u32(sm.aug(slot, 1)), &tmY, sm.bar(BB_RING2_FULL + slot), 0, i0, h, n);
   };
   auto produce = [&]() {
+    if (p.withhold_loads) return;
     if (steps > 0) {
       mbar_arrive_expect_tx(sm.bar(BB_RES_FULL), 2 * C::TILE_BYTES);
       bwd_load_tile<C>(sm.res(0), &tmK, sm.bar(BB_RES_FULL), j0, kvh, n);

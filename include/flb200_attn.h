@@ -282,6 +282,12 @@ typedef struct flb200_attn_bwd_params {
 size_t flb200_attn_bwd_workspace_bytes(const flb200_attn_bwd_params* p);
 int flb200_attn_bwd(const flb200_attn_bwd_params* p, void* cuda_stream);
 
+/* Self-test of the backward kernels' bounded waits, like flb200_selftest_wait_timeout: the kernels of `p`
+ * run with their loads withheld, every role's first wait runs into p->wait_limit_us (0 = 1000 us here),
+ * the CTAs leave through the common exit, p->status (required) receives the timeout code, dq / dk / dv
+ * are left untouched (the workspace is written).  No counterpart in the reference. */
+int flb200_selftest_bwd_wait_timeout(const flb200_attn_bwd_params* p, void* cuda_stream);
+
 /* Map the value read back from a status word to a flb200_status
  * (0 -> FLB200_OK, timeout code -> FLB200_E_TIMEOUT).  If `barrier` / `block`
  * are non-NULL they receive which wait expired and the low 16 bits of the index of the thread

@@ -120,3 +120,53 @@ def test_backward_of_strided_views():
     close(dq, rq, "dq")
     close(dk, rk, "dk")
     close(dv, rv, "dv")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_a_backward_wait_that_runs_out_ends_the_launch_with_a_status(D):
+    """The permitted form of a failure test, for the backward kernels: the self-test launch withholds
+    their loads, the roles' first waits run into the one-millisecond limit, the CTAs leave through the
+    common exit with E_TIMEOUT in the status word and its host mirror, the gradient buffers stay untouched,
+    and the next normal backward gives the same bits as the one before."""
+    import ctypes as C
+    from flashlight_b200 import _lib, ops
+    lib = _lib.load()
+    q, k, v, dout = rnd((1, 4, 512, D), 30), rnd((1, 2, 512, D), 31), rnd((1, 2, 512, D), 32), rnd((1, 4, 512, D), 33)
+    o, lse = ops.attn_fwd_lse(q, k, v, D ** -0.5, mask=_lib.MASK_CAUSAL)
+    before = ops.attn_bwd(q, k, v, o, dout, lse, D ** -0.5, True)
+    torch.cuda.synchronize()
+
+    dq, dk, dv = torch.full_like(q, 7.0), torch.full_like(k, 7.0), torch.full_like(v, 7.0)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+    p = _lib.AttnBwdParams()
+    p.struct_size = C.sizeof(_lib.AttnBwdParams)
+    p.N, p.Hq, p.Hkv, p.L, p.S, p.E = 1, 4, 2, 512, 512, D
+    for name, t in (("q", q), ("k", k), ("v", v), ("o", o), ("dout", dout), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        setattr(p, name, t.data_ptr())
+    for name, t in (("q_stride", q), ("k_stride", k), ("v_stride", v), ("o_stride", o), ("do_stride", dout),
+                    ("dq_stride", dq), ("dk_stride", dk), ("dv_stride", dv)):
+        a = getattr(p, name)
+        a[0], a[1], a[2] = t.stride(0), t.stride(1), t.stride(2)
+    p.lse_stride[0], p.lse_stride[1] = lse.stride(0), lse.stride(1)
+    p.scale, p.causal = D ** -0.5, 1
+    ws = torch.empty(lib.flb200_attn_bwd_workspace_bytes(C.byref(p)), dtype=torch.uint8, device="cuda")
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    p.status, p.status_host, p.wait_limit_us = status.data_ptr(), mirror.data_ptr(), 1000
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.flb200_selftest_bwd_wait_timeout(C.byref(p), stream) == _lib.OK
+    torch.cuda.synchronize()                        # returns: nothing hangs, nothing traps
+    word = int(status.item())
+    bar, blk = C.c_int32(-1), C.c_int32(-1)
+    assert lib.flb200_decode_status(word, C.byref(bar), C.byref(blk)) == _lib.E_TIMEOUT
+    assert 64 <= bar.value < 64 + 24                # the backward kernels number their barriers from 64
+    assert int(mirror[0]) == word
+    assert bool((dq == 7.0).all()) and bool((dk == 7.0).all()) and bool((dv == 7.0).all())
+
+    status.zero_()
+    mirror.zero_()
+    p.wait_limit_us = 0
+    assert lib.flb200_attn_bwd(C.byref(p), stream) == _lib.OK
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert all(torch.equal(a, b) for a, b in zip((dq, dk, dv), before))
