@@ -303,7 +303,7 @@ int flb200_decode_status(int32_t status_word, int32_t* barrier, int32_t* block);
  * One launch writes the three operands; the caller then runs flb200_attn_fwd on them with
  * score_mod = BIAS, bias[0] = pair_bias and scale = 1 / sqrt(c_hidden).
  * All inputs bf16 and dense: scalars [rows][C], points [rows][P][point_dim]; outputs [rows][E] / [rows_k][Ev]
- * with E >= C + 2 P_qk point_dim + 2 and Ev >= C + P_v point_dim, both multiples of 8. */
+ * with E >= C + 2 P_qk point_dim + 2 and Ev >= C + P_v point_dim, both multiples of 8, 16-byte aligned. */
 typedef struct flb200_ipa_pack_params {
   uint32_t struct_size;
   int32_t rows_q, rows_k;       /* B * H * N query rows; B * H * N_k key / value rows */
