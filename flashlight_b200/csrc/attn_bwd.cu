@@ -25,6 +25,9 @@ int validate_bwd(const flb200_attn_bwd_params* p) {
   if (!(p->scale > 0.f) || !std::isfinite(p->scale)) return FLB200_E_BAD_ARG;
   if (p->E > 128) return FLB200_E_UNSUPPORTED;  // backward kernels: head dims up to 128, q/k and v alike
   if (p->L > (1 << 24) || p->S > (1 << 24)) return FLB200_E_UNSUPPORTED;
+  // the per-row arrays of the workspace are indexed with 32-bit row numbers
+  if (static_cast<int64_t>(p->N) * p->Hq * ((static_cast<int64_t>(p->L) + 127) / 128 * 128) > 0x7fffffffLL)
+    return FLB200_E_UNSUPPORTED;
   const void* ptrs[] = {p->q, p->k, p->v, p->o, p->dout, p->dq, p->dk, p->dv};
   for (const void* x : ptrs)
     if (!aligned16(x)) return FLB200_E_MISALIGNED;
