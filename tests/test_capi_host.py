@@ -235,3 +235,31 @@ def test_ipa_pack_rejects_bad_descriptions_on_the_host(lib):
     assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
     p.k_points, p.struct_size = FAKE, 12
     assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
+
+
+def _evo(D, S=384, rows=16, heads=8):
+    """Evoformer-style description: bias 0 a key vector per row, bias 1 a pair bias shared by the rows."""
+    p = good(N=rows, Hq=heads, Hkv=heads, L=S, S=S, E=D, Ev=D)
+    for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        a = getattr(p, name)
+        a[0], a[1], a[2] = S * heads * D, D, heads * D        # [rows, S, H, D] storage
+    p.score_mod, p.bias_inner = _lib.SCORE_BIAS, rows
+    p.bias[0] = p.bias[1] = FAKE
+    for i, v in enumerate((0, S, 0, 0)):                        # strides {b, r, h, i}: one vector per row
+        p.bias_stride[0][i] = v
+    for i, v in enumerate((0, 0, S * S, S)):                    # one [S, S] matrix per head
+        p.bias_stride[1][i] = v
+    return p
+
+
+def test_optional_scratch_of_the_resident_pair_bias_kernel(lib, monkeypatch):
+    """Heads of 32 leave room for the key-vector rows beside four ring slots: 4 KB per (row, key tile);
+    heads of 64 do not, and the switch turns the path off."""
+    monkeypatch.delenv("FLB200_KEYVEC_MMA", raising=False)
+    assert lib.flb200_attn_validate(C.byref(_evo(32))) == _lib.OK
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 16 * 3 * 4096
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, S=200))) == 16 * 2 * 4096
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(64))) == 0
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, rows=2))) == 0      # fewer than four rows share the pair bias
+    monkeypatch.setenv("FLB200_KEYVEC_MMA", "0")
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 0
