@@ -293,14 +293,17 @@ ResidentPlan plan_resident(const flb200_attn_params* p, int width) {
   r.rows = rows;
   r.chunks = (R + rows - 1) / rows;
   r.use = true;
-  // Key vector through the tensor cores: one vector per row (no head axis), and an even number of at least
-  // four ring slots per stage beside the tile of ones and the slots / 2 tiles of rows per stage that
-  // travel with the K tiles (4 KB each).  It needs scratch memory from the caller; without it the
+  // Key vector through the tensor cores: one vector per row (no head axis), and an even number of ring
+  // slots per stage (K tiles in the even ones) beside the tile of ones and the slots / 2 tiles of rows per
+  // stage that travel with the K tiles (4 KB each).  Even a ring of two slots (heads of 64 with two bias
+  // tiles) measured 15 % faster with the vector on the tensor cores than three slots without.  It needs scratch memory from the caller; without it the
   // softmax threads add the vector as before.
   if (r.rowvec >= 0 && p->bias_stride[r.rowvec][2] == 0) {
     int even = std::min(6, r.slots) & ~1;
-    while (even >= 4 && 2 * even * tile_bytes + 4096 * (1 + even) > room) even -= 2;
-    bool on = even >= 4;
+    while (even >= 2 && 2 * even * tile_bytes + 4096 * (1 + even) > room) even -= 2;
+    // (a small problem, under about 6000 tile products, does not pay for the launch that lays the rows out)
+    const long long work = static_cast<long long>(p->N) * p->Hq * ((p->L + kTileM - 1) / kTileM) * nt;
+    bool on = even >= 2 && work >= 6144;
     if (const char* e = std::getenv("FLB200_KEYVEC_MMA")) on = on && std::atoi(e) != 0;
     if (on) {
       r.keyvec_bytes = static_cast<size_t>(p->N) * nt * 4096;

@@ -237,7 +237,7 @@ def test_ipa_pack_rejects_bad_descriptions_on_the_host(lib):
     assert lib.flb200_ipa_pack(C.byref(p), None) == _lib.E_BAD_ARG
 
 
-def _evo(D, S=384, rows=16, heads=8):
+def _evo(D, S=384, rows=256, heads=8):
     """Evoformer-style description: bias 0 a key vector per row, bias 1 a pair bias shared by the rows."""
     p = good(N=rows, Hq=heads, Hkv=heads, L=S, S=S, E=D, Ev=D)
     for name in ("q_stride", "k_stride", "v_stride", "o_stride"):
@@ -253,13 +253,15 @@ def _evo(D, S=384, rows=16, heads=8):
 
 
 def test_optional_scratch_of_the_resident_pair_bias_kernel(lib, monkeypatch):
-    """Heads of 32 leave room for the key-vector rows beside four ring slots: 4 KB per (row, key tile);
-    heads of 64 do not, and the switch turns the path off."""
+    """4 KB of key-vector rows per (row, key tile) wherever an even number of ring slots fits beside them:
+    heads of 32, heads of 64 with two bias tiles but not with three; the switch turns the path off."""
     monkeypatch.delenv("FLB200_KEYVEC_MMA", raising=False)
     assert lib.flb200_attn_validate(C.byref(_evo(32))) == _lib.OK
-    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 16 * 3 * 4096
-    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, S=200))) == 16 * 2 * 4096
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 256 * 3 * 4096
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, S=200))) == 256 * 2 * 4096
     assert lib.flb200_attn_workspace_bytes(C.byref(_evo(64))) == 0
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(64, S=256))) == 256 * 2 * 4096
     assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, rows=2))) == 0      # fewer than four rows share the pair bias
+    assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, rows=16, heads=2))) == 0   # too little work for one more launch
     monkeypatch.setenv("FLB200_KEYVEC_MMA", "0")
     assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 0

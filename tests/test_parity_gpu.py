@@ -233,11 +233,13 @@ def test_evoformer(D, S, stages):
     check(av.attention_reference(q, k, v, []), ao.evoformer(q, k, v, []))
 
 
-def test_evoformer_key_vector_added_by_the_tensor_cores(monkeypatch):
-    """Resident pair-bias kernel (four or more rows share a pair bias, narrow heads): the per-row key
-    vector, with its -inf entries, is added by one more k-step of the score product when the caller gives
-    scratch memory (one launch more: the kernel that lays the vector out), by the softmax threads otherwise."""
-    B, N, H, S, D = 2, 6, 4, 328, 32   # rows of the pair bias start on 16-byte boundaries (TMA)
+@pytest.mark.parametrize("D,S", [(32, 328), (64, 256), (64, 200)])
+def test_evoformer_key_vector_added_by_the_tensor_cores(D, S, monkeypatch):
+    """Resident pair-bias kernel (four or more rows share a pair bias, narrow heads, enough work to pay for
+    one more launch): the per-row key vector, with its -inf entries, is added by one more k-step of the
+    score product when the caller gives scratch memory (the second launch lays the vector out), by the
+    softmax threads otherwise.  Heads of 64 run it on a ring of two slots per stage."""
+    B, N, H = 2, 200, 4   # enough rows to pay for the extra launch; bias rows start on 16-byte boundaries (TMA)
     q, k, v = rnd((B, N, S, H, D), 60), rnd((B, N, S, H, D), 61), rnd((B, N, S, H, D), 62)
     pair = rnd((B, 1, H, S, S), 63)
     g = torch.Generator().manual_seed(64)
@@ -252,7 +254,9 @@ def test_evoformer_key_vector_added_by_the_tensor_cores(monkeypatch):
         outs[flag] = av.attention_reference(q, k, v, [vec, pair])
         assert flashlight_b200.launch_count() - n0 == launches
         check(outs[flag], ref, flag)
-    assert (outs["1"].float() - outs["0"].float()).abs().max().item() <= 2e-2
+    # the two paths round independently: up to one bf16 step apart on top of the flat band
+    a, b = outs["1"].float(), outs["0"].float()
+    assert bool(((a - b).abs() <= 2e-2 + 2.0 ** -7 * b.abs()).all())
 
 
 # ---------------------------------------------------------------- the reference tests' own inputs
