@@ -150,7 +150,7 @@ int attn_bwd_impl(const flb200_attn_bwd_params* p, void* cuda_stream, bool withh
   if (make_tmap_bf16_4d(&tmX, xrows, 16, lp, p->Hq, p->N, 16, lp * 16, lp * 16 * p->Hq, 16, 128) ||
       make_tmap_bf16_4d(&tmY, yrows, 16, lp, p->Hq, p->N, 16, lp * 16, lp * 16 * p->Hq, 16, 128))
     return FLB200_E_LAUNCH;
-  attn_bwd_delta_kernel<<<rows / 16, 256, 0, stream>>>(
+  attn_bwd_delta_kernel<<<rows / 64, 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->dout), p->o_stride[0],
       p->o_stride[1], p->o_stride[2], p->do_stride[0], p->do_stride[1], p->do_stride[2], p->E, p->Hq, p->L, bp.Lp,
       bp.delta, p->lse, p->lse_stride[0], p->lse_stride[1], 1.0f / p->scale, reinterpret_cast<uint4*>(xrows),

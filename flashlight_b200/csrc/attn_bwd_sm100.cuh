@@ -248,42 +248,58 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, const
                                       int64_t do_sl, int E, int Hq, int L, int Lp, float* __restrict__ delta,
                                       const float* __restrict__ lse, int64_t lse_sn, int64_t lse_sh, float inv_scale,
                                       uint4* __restrict__ xrows, uint4* __restrict__ yrows) {
-  // 16 lanes per (n, h, i) row, 8 features (one 16-byte load per tensor) per lane; rows start on 16-byte
-  // boundaries (pointers and strides are checked by the host)
-  const int row = blockIdx.x * 16 + (threadIdx.x >> 4);
+  // 16 lanes per (n, h, i) row, 8 features (one 16-byte load per tensor) per lane, four consecutive rows
+  // per lane group with their eight loads in flight together; rows start on 16-byte boundaries (pointers
+  // and strides are checked by the host; the padded row count is a multiple of 128)
+  constexpr int kRows = 4;
+  const int row0 = (blockIdx.x * 16 + (threadIdx.x >> 4)) * kRows;
   const int sub = threadIdx.x & 15;
-  const int i = row % Lp, nh = row / Lp, h = nh % Hq, n = nh / Hq;
-  float acc = 0.f;
   const int d = sub * 8;
-  if (i < L && d < E) {
-    const __nv_bfloat16* po = o + n * o_sn + h * o_sh + i * o_sl + d;
-    const __nv_bfloat16* pd = d_o + n * do_sn + h * do_sh + i * do_sl + d;
-    if (d + 8 <= E) {
-      const uint4 a = *reinterpret_cast<const uint4*>(po), b = *reinterpret_cast<const uint4*>(pd);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  const int nh = row0 / Lp, h = nh % Hq, n = nh / Hq, i0 = row0 % Lp;   // the four rows share (n, h)
+  const __nv_bfloat16* po = o + n * o_sn + h * o_sh + d;
+  const __nv_bfloat16* pd = d_o + n * do_sn + h * do_sh + d;
+  uint4 a[kRows], b[kRows];
+  const bool vec = d + 8 <= E;
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    a[r] = b[r] = make_uint4(0, 0, 0, 0);
+    if (vec && i0 + r < L) {
+      a[r] = *reinterpret_cast<const uint4*>(po + (i0 + r) * o_sl);
+      b[r] = *reinterpret_cast<const uint4*>(pd + (i0 + r) * do_sl);
+    }
+  }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) {
+    const int i = i0 + r, row = row0 + r;
+    float acc = 0.f;
+    if (vec) {
+      const uint32_t aw[4] = {a[r].x, a[r].y, a[r].z, a[r].w}, bw[4] = {b[r].x, b[r].y, b[r].z, b[r].w};
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         // a bf16 is the upper half of an fp32
         acc = fmaf(__uint_as_float(aw[w] << 16), __uint_as_float(bw[w] << 16), acc);
         acc = fmaf(__uint_as_float(aw[w] & 0xffff0000u), __uint_as_float(bw[w] & 0xffff0000u), acc);
       }
-    } else {
-      for (int e = 0; d + e < E; ++e) acc = fmaf(__bfloat162float(po[e]), __bfloat162float(pd[e]), acc);
+    } else if (i < L && d < E) {
+      for (int e = 0; d + e < E; ++e)
+        acc = fmaf(__bfloat162float(po[i * o_sl + e]), __bfloat162float(pd[i * do_sl + e]), acc);
     }
-  }
 #pragma unroll
-  for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  // the rows of the extra k-step of the dK/dV kernel: [hi, lo, 0 x 14] of -lse / scale and of -delta
-  // (rows of the padding beyond L: zeros; their Q and dO rows are zero-filled, so they contribute nothing)
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  if (sub == 0) {
-    delta[row] = acc;
-    yrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(-acc) : 0u, 0, 0, 0);
-    yrows[2 * static_cast<int64_t>(row) + 1] = zero;
-  } else if (sub == 1) {
-    const float x = i < L ? -lse[n * lse_sn + h * lse_sh + i] * inv_scale : 0.f;
-    xrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(x) : 0u, 0, 0, 0);
-    xrows[2 * static_cast<int64_t>(row) + 1] = zero;
+    for (int s = 8; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    // the rows of the extra k-step of the dK/dV kernel: [hi, lo, 0 x 14] of -lse / scale and of -delta
+    // (rows of the padding beyond L: zeros; their Q and dO rows are zero-filled, so they contribute nothing)
+    if (sub == 0) {
+      delta[row] = acc;
+      yrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(-acc) : 0u, 0, 0, 0);
+    } else if (sub == 1) {
+      yrows[2 * static_cast<int64_t>(row) + 1] = zero;
+    } else if (sub == 2) {
+      const float x = i < L ? -lse[n * lse_sn + h * lse_sh + i] * inv_scale : 0.f;
+      xrows[2 * static_cast<int64_t>(row)] = make_uint4(i < L ? split_bf16_pair(x) : 0u, 0, 0, 0);
+    } else if (sub == 3) {
+      xrows[2 * static_cast<int64_t>(row) + 1] = zero;
+    }
   }
 }
 
