@@ -38,7 +38,7 @@ namespace flb {
 template <int E_, int EV_, int SCORE_, int MASK_, int DIFF_, int STAGES_ = 2>
 struct AttnCfg {
   static constexpr int E = E_, EV = EV_, SCORE = SCORE_, MASK = MASK_;
-  static constexpr bool DIFF = DIFF_ != 0;  // differential attention: 1 = P as one bf16 term, 2 = as two
+  static constexpr bool DIFF = DIFF_ != 0;  // differential attention: 1 = P as one bf16 term, 2 = as two, 3 = fp16
   // Query tiles per CTA.  Two: 512 threads, all of tensor memory, one CTA per SM, the stages share
   // every K/V tile.  One: 256 threads, half of tensor memory and of shared memory, two CTAs per
   // SM that run independently, so one CTA's set-up and epilogue hide behind the other's tiles
@@ -57,6 +57,9 @@ struct AttnCfg {
   // 1.0e-4), and the second would cost 8 of 20 MMA steps per tile and the tile tried with the running
   // maximum: the kernel is built both ways.
   static constexpr bool SPLIT_P = DIFF_ == 2;
+  // 3: P as one fp16 term against V converted to fp16 in shared memory (11 mantissa bits for 12 k-steps
+  // a tile instead of 16 bits for 20)
+  static constexpr bool PV_F16 = DIFF_ == 3;
   // ALiBi's bias grows along the keys, so a walk from the first key tile up would raise every
   // row maximum tile after tile and rescale the accumulator each time.  Walking the tiles from
   // the last one down meets the largest bias first; the result does not depend on the order.
@@ -142,7 +145,9 @@ enum : int {
   BAR_O_FREE = BAR_O_STAGED,   // +s   epilogue -> MMA / softmax: the row's accumulator and row sums are read
   BAR_RING_FULL = 14,          // +8s+slot  (14..20 and 22..28)
   BAR_BIAS_FULL = 21,          //      producer -> softmax: the pair-bias tiles are in shared memory
-  BAR_RING_EMPTY = 32          // +8s+slot  (32..38 and 40..46)
+  BAR_RING_EMPTY = 32,         // +8s+slot  (32..38 and 40..46)
+  // fp16 P.V (differential attention): converter warps -> MMA, the V tile of a slot is fp16 now
+  BAR_V_CONV = 32              // +slot
 };
 
 struct TileRange {
@@ -477,7 +482,7 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
                       const TileRange (&rg)[2], int lo, int hi) {
   const uint32_t leader = elect_one() ? 1u : 0u;  // the lane that issues; all lanes run the loop
   constexpr uint32_t idesc_qk = make_idesc_bf16(128, kTileN, 0, C::KT ? 1 : 0);
-  constexpr uint32_t idesc_pv = make_idesc_bf16(128, C::EV, 0, 1);
+  constexpr uint32_t idesc_pv = C::PV_F16 ? make_idesc_f16(128, C::EV, 0, 1) : make_idesc_bf16(128, C::EV, 0, 1);
   const uint32_t tS[2] = {tmem + C::COL_S0, tmem + C::COL_S1};
   const uint32_t tO[2] = {tmem + C::COL_O0, tmem + C::COL_O1};
   [[maybe_unused]] const uint32_t tP[2] = {tmem + C::COL_P0, tmem + C::COL_P1};
@@ -518,6 +523,9 @@ FLB_DEV void mma_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& p,
     const uint32_t v_lo = v_lo0 + slot0 + vslot * (C::SLOT_BYTES >> 4);
     const uint32_t k_lo = k_lo0 + slot0 + kslot * (C::SLOT_BYTES >> 4);
     if (have_v) FLB_WAIT(sm, BAR_KV_FULL + vslot, vph);
+    if constexpr (C::PV_F16) {
+      if (have_v) FLB_WAIT(sm, BAR_V_CONV + vslot, vph);   // the V tile has been rewritten as fp16
+    }
     if (have_k) FLB_WAIT(sm, BAR_KV_FULL + kslot, kph);
 #pragma unroll
     for (int s = 0; s < C::STAGES; ++s) {
@@ -931,7 +939,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
             pr.y = ex2(x.y);
           }
           if (idx & 2) sumb = __fadd2_rn(sumb, pr); else suma = __fadd2_rn(suma, pr);
-          pk[idx >> 1] = pack_bf16(pr.x, pr.y);
+          pk[idx >> 1] = C::PV_F16 ? pack_f16_sat(pr.x, pr.y) : pack_bf16(pr.x, pr.y);
         }
         const float lt = (suma.x + suma.y) + (sumb.x + sumb.y);
         if (__all_sync(0xffffffffu, lt <= kSpeculateSumLimit)) {
@@ -1028,7 +1036,7 @@ FLB_DEV void softmax_role(const Smem<C>& sm, uint32_t tmem, const KernelParams& 
           pr.y = ex2(x.y);
         }
         if (c & 2) sumb = __fadd2_rn(sumb, pr); else suma = __fadd2_rn(suma, pr);
-        const uint32_t hi = pack_bf16(pr.x, pr.y);
+        const uint32_t hi = C::PV_F16 ? pack_f16_sat(pr.x, pr.y) : pack_bf16(pr.x, pr.y);
         pk[c >> 1] = hi;
         if constexpr (C::SPLIT_P) {
           // second bf16 term p - bf16(p): P = hi + lo carries 16 mantissa bits into the PV product
@@ -1115,6 +1123,40 @@ FLB_DEV void pointwise_role(const Smem<C>& sm, uint32_t tmem, const KernelParams
   }
   sm.scale(s)[row] = 1.0f;  // the epilogue's normalisation becomes a copy
   mbar_arrive(sm.bar(BAR_SCALE_FULL + s));
+}
+
+// ------------------------------------------------------------------------------------------
+// fp16 P.V (differential attention with the RMS normalisation): the epilogue warps, idle until the last
+// tile, rewrite every V tile in place as fp16 while the score products and the softmax of the tile run
+// (a bf16 value is an fp16 value wherever the fp16 range holds it: V is first multiplied by the power of
+// two that puts the tensor's largest magnitude at 2^13..2^14, which the RMS normalisation cancels).
+// The tile is 128 rows of 128-byte swizzled boxes: element positions do not matter here, each thread
+// converts 16-byte chunks where they lie.
+// ------------------------------------------------------------------------------------------
+template <class C>
+FLB_DEV void convert_v_role(const Smem<C>& sm, const KernelParams& p, int lo, int hi) {
+  static_assert(!C::PV_F16 || C::NSTAGE % 2 == 0, "V tiles must keep to the odd slots of the ring");
+  const int tid = threadIdx.x & 127;
+  const int n_pos = hi - lo;
+  const float f = v_scale_from_absmax(*p.v_absmax);
+#pragma unroll 1
+  for (int t = 0; t < n_pos; ++t) {
+    const int vseq = 2 * t + 1;
+    const int vslot = vseq % C::NSTAGE;
+    const uint32_t vph = (vseq / C::NSTAGE) & 1;
+    FLB_WAIT(sm, BAR_KV_FULL + vslot, vph);
+    uint4* tile = reinterpret_cast<uint4*>(sm.slot(vslot));
+#pragma unroll 4
+    for (int c = tid; c < C::V_BYTES / 16; c += 128) {
+      uint4 w = tile[c];
+      uint32_t* ww = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ww[e] = pack_f16_sat(u2f(ww[e] << 16) * f, u2f(ww[e] & 0xffff0000u) * f);
+      tile[c] = w;
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(sm.bar(BAR_V_CONV + vslot));
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1217,7 +1259,13 @@ FLB_DEV void epilogue_role(const Smem<C>& sm, uint32_t tmem, const CUtensorMap* 
       }
       ss += sm.xchg()[row];
     }
-    const float rs = p.rms_norm ? rsqrtf(ss * p.inv_ev + p.rms_eps) : 1.0f;
+    float eps = p.rms_eps;
+    if constexpr (C::PV_F16) {
+      // the accumulators carry V's power-of-two factor f: eps * f^2 keeps x * rsqrt(mean(x^2) + eps) as it was
+      const float f = v_scale_from_absmax(*p.v_absmax);
+      eps *= f * f;
+    }
+    const float rs = p.rms_norm ? rsqrtf(ss * p.inv_ev + eps) : 1.0f;
     uint8_t* tile = sm.q(0);  // both Q tiles (2 * 128 * E * 2 bytes = one 128 x EV output tile)
     static_assert(2 * C::Q_BYTES >= 128 * C::EV * 2, "output tile does not fit the Q tiles");
 #pragma unroll
@@ -1401,6 +1449,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool single = C::ROWLOOP && lane >= BAR_Q_EMPTY && lane < BAR_Q_EMPTY + 2;
       mbar_init(sm.bar(lane), all_threads && !single ? 128 : 1);  // 128 arriving threads, or one commit / TMA
       if (C::ROWLOOP && lane < 16) mbar_init(sm.bar(32 + lane), 1);  // ring slots handed back by commits
+      if (C::PV_F16 && lane < 8) mbar_init(sm.bar(BAR_V_CONV + lane), 128);
     }
     if (C::DIFF && lane == 0) mbar_init(sm.xbar(), 128);
     fence_mbar_init();
@@ -1450,6 +1499,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if constexpr (C::STAGES == 1) epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else if (C::STAGES == 2 && warp < 12) {
     reg_dec<kRegsEpilogue>();
+    if constexpr (C::PV_F16) convert_v_role<C>(sm, p, lo, hi);
     if constexpr (C::ROWLOOP) epilogue_role_rows<C>(sm, tmem, &tmO, p, rb_h, r0[0], rw);
     else epilogue_role<C>(sm, tmem, &tmO, p, n, h, vcol0, r0, rg, lo, hi);
   } else {

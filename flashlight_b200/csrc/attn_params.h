@@ -83,6 +83,10 @@ struct KernelParams {
   float lambda;
   int rms_norm;
   float rms_eps;
+  // fp16 P.V of differential attention: bits of max |v| over the whole V tensor, found by v_absmax_kernel;
+  // V is multiplied by the power of two that brings that maximum to [2^13, 2^14) on its way to fp16
+  // (the RMS normalisation makes the result independent of it, eps scaled alike)
+  const uint32_t* v_absmax;
   float inv_ev;     // 1 / (true value width): the mean of the RMS normalisation
   int v_halves;     // 2: value heads wider than the kernel; CTA pairs take one half of the columns each
   int v_exchange;   // the two CTAs of a pair run as a cluster and swap their rows' sums of squares

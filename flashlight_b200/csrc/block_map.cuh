@@ -130,4 +130,45 @@ __global__ void keyvec_rows_kernel(const __nv_bfloat16* __restrict__ bias, int64
   out[2 * idx + (swap ^ 1)] = make_uint4(0, 0, 0, 0);
 }
 
+// max |v| over a [N][H][S][Ev] bf16 tensor (feature axis contiguous), as the bits of a non-negative float
+// (their integer order is the order of the values; a NaN lands above infinity).  blockIdx.y = (n, h);
+// sixteen lanes per row, one 16-byte load each (Ev <= 128), the blocks of a head stride over its rows.
+__global__ void v_absmax_kernel(const __nv_bfloat16* __restrict__ v, int64_t sn, int64_t sh, int64_t ss, int H, int S,
+                                int Ev, uint32_t* __restrict__ out) {
+  const int n = blockIdx.y / H, h = blockIdx.y % H;
+  const int c = threadIdx.x & 15;
+  const unsigned short* base = reinterpret_cast<const unsigned short*>(v + n * sn + h * sh);
+  uint32_t m = 0;
+  if (c * 8 < Ev) {
+    const int step = gridDim.x * 16;
+    const bool vec = c * 8 + 8 <= Ev;
+    for (int j = blockIdx.x * 16 + (threadIdx.x >> 4); j < S; j += 4 * step) {
+      // four rows per trip, their loads in flight together
+      uint4 w[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        w[r] = make_uint4(0, 0, 0, 0);
+        const int jr = j + r * step;
+        if (jr < S) {
+          const unsigned short* row = base + static_cast<int64_t>(jr) * ss;
+          if (vec) {
+            w[r] = *reinterpret_cast<const uint4*>(row + c * 8);   // rows start on 16-byte boundaries
+          } else {
+            for (int e = c * 8; e < Ev; ++e) m = max(m, (static_cast<uint32_t>(row[e]) << 16) & 0x7fffffffu);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t ww[4] = {w[r].x, w[r].y, w[r].z, w[r].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) m = max(m, max((ww[e] << 16) & 0x7fffffffu, ww[e] & 0x7fff0000u));
+      }
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+  if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(out, m);
+}
+
 }  // namespace flb

@@ -241,6 +241,14 @@ int pick_stages(const flb200_attn_params* p) {
 // (row stride 0) and at most one key vector per row (query stride 0).  Such a problem runs on the
 // resident-bias kernel: a CTA keeps the pair-bias columns of its (head, query tile) in shared
 // memory and walks a range of rows.  FLB200_BIAS_RESIDENT=0 turns the choice off for tuning.
+// differential attention whose P.V product can run in fp16: RMS-normalised (the result does not depend on
+// V's scale), one CTA per work item (value heads up to 128)
+bool diff_pv_f16_eligible(const flb200_attn_params* p, int width) {
+  if (!p->diff || !p->diff_rms_norm || width == 128 || p->Ev > 2 * width) return false;
+  if (const char* e = std::getenv("FLB200_DIFF_PV_F16")) return std::atoi(e) != 0;
+  return true;
+}
+
 struct ResidentPlan {
   bool use = false;
   int pair = -1, rowvec = -1;  // indices into p->bias
@@ -417,6 +425,11 @@ size_t flb200_attn_workspace_bytes(const flb200_attn_params* p) {
     // optional scratch of the resident pair-bias kernel (the call also runs without it)
     const int width = kernel_width(p->E, p->Ev, kernel_score(p), p->mask, p->diff);
     return width ? plan_resident(p, width).keyvec_bytes : 0;
+  }
+  if (p->diff && p->mask != FLB200_MASK_DOCUMENT && validate(p) == FLB200_OK) {
+    // optional scratch of the fp16 P.V path of differential attention (one word: max |v|)
+    const int width = kernel_width(p->E, p->Ev, kernel_score(p), p->mask, p->diff);
+    return width && diff_pv_f16_eligible(p, width) ? 256 : 0;
   }
   if (p->mask != FLB200_MASK_DOCUMENT) return 0;
   return map_layout(p).total;
@@ -620,7 +633,25 @@ int attn_fwd_impl(const flb200_attn_params* p, void* cuda_stream, bool withhold_
 #define FLB_DIFF(E, EV)                                                                                     \
   (split ? dispatch_mods<E, EV, 2, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream)               \
          : dispatch_mods<E, EV, 1, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream))
-    if (width == 128) e = FLB_DIFF(128, 128);
+    // With the RMS normalisation and scratch from the caller, P.V runs in fp16 (one term of 11 mantissa bits
+    // against V rewritten as fp16 in shared memory) instead of two bf16 terms: 12 k-steps a tile for 20.
+    bool pv_f16 = diff_pv_f16_eligible(p, width) && split && p->workspace && p->workspace_bytes >= 16 &&
+                  aligned16(p->workspace);
+    if (pv_f16) {
+      uint32_t* absmax = static_cast<uint32_t*>(p->workspace);
+      if (cudaMemsetAsync(absmax, 0, sizeof(uint32_t), stream) != cudaSuccess) return FLB200_E_LAUNCH;
+      // about eight waves of blocks over the heads' rows
+      const int per_head = std::max(1, std::min((p->S + 63) / 64, (148 * 8 + p->N * H - 1) / (p->N * H)));
+      v_absmax_kernel<<<dim3(per_head, p->N * H), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(p->v),
+                                                                   p->v_stride[0], p->v_stride[1], p->v_stride[2], H,
+                                                                   p->S, p->Ev, absmax);
+      if (cudaGetLastError() != cudaSuccess) return FLB200_E_LAUNCH;
+      flb::count_launches(1);
+      kp.v_absmax = absmax;
+    }
+    if (pv_f16 && width == 64) e = dispatch_mods<64, 128, 3, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (pv_f16) e = dispatch_mods<32, 64, 3, 2>(sc, mk, tmQ, tmK, tmV, tmO, kp, grid, cluster, stream);
+    else if (width == 128) e = FLB_DIFF(128, 128);
     else if (width == 64) e = FLB_DIFF(64, 128);
     else e = FLB_DIFF(32, 64);
 #undef FLB_DIFF

@@ -247,6 +247,13 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
          (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// The same for fp16 inputs on BOTH sides (A and B formats 0).  Operand formats are never mixed: a product
+// with an fp16 A and a bf16 B operand is an illegal instruction on this part.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
 // ----------------------------------------------------------------------------
 // tcgen05.mma (single issuing thread), commit
 // ----------------------------------------------------------------------------
@@ -471,6 +478,13 @@ FLB_DEV uint32_t pack_bf16(float lo, float hi) {
   return y;
 }
 
+// {lo, hi} -> packed fp16x2 with lo in bits [0,16); values beyond the fp16 range saturate
+FLB_DEV uint32_t pack_f16_sat(float lo, float hi) {
+  uint32_t y;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(y) : "f"(hi), "f"(lo));
+  return y;
+}
+
 // hi + lo = v to about 16 bits, packed {lo half: hi term, hi half: lo term}; a non-finite v gives
 // (-inf, 0): a score it is added to becomes -inf, its exponential 0
 FLB_DEV uint32_t split_bf16_pair(float v) {
@@ -498,6 +512,15 @@ FLB_DEV float2 exp2_poly2(float2 x) {
   q.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23));
   q.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23));
   return q;
+}
+
+// The power of two 2^k, k in [-60, 60], that brings a maximum with these bits to [2^13, 2^14); 1 for a zero
+// or non-finite maximum.
+FLB_DEV float v_scale_from_absmax(uint32_t bits) {
+  const int e = static_cast<int>(bits >> 23);
+  if (bits == 0 || e == 0 || e >= 255) return 1.0f;
+  const int k = max(-60, min(60, 13 - (e - 127)));
+  return __uint_as_float(static_cast<uint32_t>(k + 127) << 23);
 }
 
 }  // namespace flb

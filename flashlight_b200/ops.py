@@ -242,8 +242,9 @@ def _attn_fwd_impl(q, k, v, scale, score_mod, alibi_heads, alibi_head0, softcap,
             ws.record_stream(cur)
             keep.append(ws)
             p.workspace, p.workspace_bytes, p.block_map_ready = ws.data_ptr(), ws.numel(), 1
-        elif score_mod == _lib.SCORE_BIAS:
-            # optional scratch of the resident pair-bias kernel (its key-vector rows); stream-ordered
+        elif score_mod == _lib.SCORE_BIAS or diff:
+            # optional scratch: key-vector rows of the resident pair-bias kernel, or the word that takes max |v|
+            # for the fp16 P.V product of differential attention; stream-ordered
             # like every other temporary of this call
             nbytes = lib.flb200_attn_workspace_bytes(C.byref(p))
             if nbytes:

@@ -140,7 +140,11 @@ typedef struct flb200_attn_params {
    * SCORE_BIAS: optional.  When one bias is a pair bias shared by bias_inner >= 4 rows and the other a
    * key vector per row, heads are narrow and flb200_attn_workspace_bytes() bytes (16-byte aligned) are
    * given, a small kernel lays the key vector out there and the tensor cores add it to the scores;
-   * with workspace == NULL the same result comes from the softmax threads, more slowly. */
+   * with workspace == NULL the same result comes from the softmax threads, more slowly.
+   * diff with diff_rms_norm and value heads up to 128: optional too.  Given flb200_attn_workspace_bytes()
+   * bytes, a small kernel finds max |v|, the forward kernel rewrites each V tile in shared memory as fp16
+   * times the power of two that centres V's range (the normalisation cancels it, eps is scaled alike) and
+   * P.V runs in fp16; without scratch P goes as two bf16 terms (same tolerance, 25 % slower). */
   void* workspace;
   size_t workspace_bytes;
   int32_t block_map_ready;
@@ -196,7 +200,7 @@ const char* flb200_strerror(int status);
 int flb200_attn_validate(const flb200_attn_params* p);
 
 /* Device scratch bytes flb200_attn_fwd takes for `p`: required for mask == DOCUMENT, optional for
- * SCORE_BIAS (see `workspace`), 0 otherwise.  Returns 0 for a NULL or invalid description. */
+ * SCORE_BIAS and for RMS-normalised differential attention (see `workspace`), 0 otherwise.  Returns 0 for a NULL or invalid description. */
 size_t flb200_attn_workspace_bytes(const flb200_attn_params* p);
 
 /* Build the document-mask block map into p->workspace on `cuda_stream`. */

@@ -265,3 +265,24 @@ def test_optional_scratch_of_the_resident_pair_bias_kernel(lib, monkeypatch):
     assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32, rows=16, heads=2))) == 0   # too little work for one more launch
     monkeypatch.setenv("FLB200_KEYVEC_MMA", "0")
     assert lib.flb200_attn_workspace_bytes(C.byref(_evo(32))) == 0
+
+
+def test_optional_scratch_of_rms_normalised_differential_attention(lib, monkeypatch):
+    """With the RMS normalisation and value heads up to 128 the P.V product can run in fp16: the call takes
+    256 bytes of scratch for the word that receives max |v|; wider value heads (pairs of CTAs), no
+    normalisation or the switch: none."""
+    monkeypatch.delenv("FLB200_DIFF_PV_F16", raising=False)
+    def diff(E, Ev, rms):
+        p = good(Hq=8, Hkv=8, E=E, Ev=Ev, diff=1, diff_lambda=0.8, diff_rms_norm=rms, diff_rms_eps=1e-5)
+        p.k_stride[0], p.k_stride[1], p.k_stride[2] = 8 * 256 * E, 256 * E, E
+        p.q_stride[0], p.q_stride[1], p.q_stride[2] = 8 * 256 * E, 256 * E, E
+        p.v_stride[0], p.v_stride[1], p.v_stride[2] = 4 * 256 * Ev, 256 * Ev, Ev
+        p.o_stride[0], p.o_stride[1], p.o_stride[2] = 4 * 256 * Ev, 256 * Ev, Ev
+        return p
+    assert lib.flb200_attn_validate(C.byref(diff(64, 128, 1))) == _lib.OK
+    assert lib.flb200_attn_workspace_bytes(C.byref(diff(64, 128, 1))) == 256
+    assert lib.flb200_attn_workspace_bytes(C.byref(diff(32, 64, 1))) == 256
+    assert lib.flb200_attn_workspace_bytes(C.byref(diff(64, 128, 0))) == 0
+    assert lib.flb200_attn_workspace_bytes(C.byref(diff(128, 256, 1))) == 0
+    monkeypatch.setenv("FLB200_DIFF_PV_F16", "0")
+    assert lib.flb200_attn_workspace_bytes(C.byref(diff(64, 128, 1))) == 0

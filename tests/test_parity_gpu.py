@@ -440,6 +440,28 @@ def test_diff_attention_reference_test_shape():
     check(out, ref)
 
 
+@pytest.mark.parametrize("d", [32, 64])
+@pytest.mark.parametrize("v_exp", [0, -10, 8, -30])
+def test_diff_rms_product_in_fp16_whatever_the_scale_of_v(d, v_exp, monkeypatch):
+    """RMS-normalised differential attention with value heads up to 128 runs P.V in fp16 when the caller
+    gives scratch (one launch more: the pass that finds max |v|): V is rewritten as fp16 in shared memory
+    after a multiplication by the power of two that centres its range, and eps is scaled alike, so the
+    result follows the oracle for V of any magnitude (2^-10: eps dominates the mean square; 2^-30: below
+    the fp16 range before the scaling).  Switched off, P goes as two bf16 terms."""
+    q, k = rnd((1, 6, 520, d), 90), rnd((1, 6, 520, d), 91)
+    v = (rnd((1, 3, 520, 2 * d), 92).float() * 2.0 ** v_exp).to(torch.bfloat16)
+    # with eps = 0 the result is of order one whatever the scale, so the smallest V really tests the scaling
+    kw = dict(lambda_full=0.8, is_causal=True, rms_norm=True, rms_eps=0.0 if v_exp == -30 else 1e-5)
+    ref = ao.diffattn(q, k, v, **kw)
+    assert ref.abs().mean().item() > 0.1 or v_exp == -10
+    for flag, launches in (("1", 2), ("0", 1)):
+        monkeypatch.setenv("FLB200_DIFF_PV_F16", flag)
+        n0 = flashlight_b200.launch_count()
+        out = av.diffattn(q, k, v, **kw)
+        assert flashlight_b200.launch_count() - n0 == launches
+        check(out, ref, (flag, v_exp))
+
+
 def test_diff_rms_norm_divides_by_the_true_width():
     q, k, v = rnd((1, 4, 300, 48), 86), rnd((1, 4, 300, 48), 87), rnd((1, 2, 300, 96), 88)
     check(av.diffattn(q, k, v, lambda_full=0.5, rms_norm=True), ao.diffattn(q, k, v, lambda_full=0.5, rms_norm=True))
