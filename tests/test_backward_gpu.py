@@ -170,3 +170,30 @@ def test_a_backward_wait_that_runs_out_ends_the_launch_with_a_status(D):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert all(torch.equal(a, b) for a, b in zip((dq, dk, dv), before))
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_backward_on_seeded_random_shapes(seed):
+    """Random batch, group size, lengths (queries and keys alike under the causal mask, free otherwise) and
+    head dims up to 128 in steps of 8."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g).item())
+    causal = seed % 2 == 0
+    N, Hkv, G = ri(1, 3), ri(1, 3), ri(1, 4)
+    D = 8 * ri(1, 16)
+    L = ri(1, 700)
+    S = L if causal else ri(1, 700)
+    q, k, v = rnd((N, Hkv * G, L, D), 40 + seed), rnd((N, Hkv, S, D), 140 + seed), rnd((N, Hkv, S, D), 240 + seed)
+    dout = rnd((N, Hkv * G, L, D), 340 + seed)
+    if causal:
+        fn = lambda a, b, c: av.attention_pytorch_causal(a, b, c, enable_gqa=True)
+        fo = lambda a, b, c: ao.causal(a, b, c, enable_gqa=True)
+    else:
+        fn = lambda a, b, c: av.attention_pytorch(a, b, c, enable_gqa=True)
+        fo = lambda a, b, c: ao.vanilla(a, b, c, enable_gqa=True)
+    _, dq, dk, dv = grads(fn, q, k, v, dout)
+    _, rq, rk, rv = grads(fo, q.float(), k.float(), v.float(), dout.float())
+    what = (N, Hkv, G, L, S, D, causal)
+    close(dq, rq, ("dq",) + what)
+    close(dk, rk, ("dk",) + what)
+    close(dv, rv, ("dv",) + what)
