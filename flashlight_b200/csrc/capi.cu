@@ -693,6 +693,11 @@ int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream) {
     q.workspace = scratch;
     q.workspace_bytes = FLB200_NOALLOC_SCRATCH_BYTES;
     q.block_map_ready = 0;  // the array holds whatever the previous call left: always rebuild
+  } else {
+    // the workspace fields are ignored here: the optional-scratch paths (key vector and fp16 P.V through
+    // the tensor cores) stay off, whatever the caller left in them
+    q.workspace = nullptr;
+    q.workspace_bytes = 0;
   }
   return flb200_attn_fwd(&q, cuda_stream);
 }

@@ -231,7 +231,8 @@ int flb200_attn_fwd(const flb200_attn_params* p, void* cuda_stream);
  *  - All calls on a device share the one array and the map is rebuilt on every call.  Two
  *    calls whose kernels can overlap on the GPU (different streams without ordering) race on
  *    it; keep such calls on one stream or order them with events.
- *  - Masks other than DOCUMENT need no scratch and are simply forwarded.
+ *  - Masks other than DOCUMENT need no scratch and are forwarded with the workspace fields cleared (the
+ *    paths that use optional scratch stay off).
  */
 int flb200_attn_fwd_noalloc(const flb200_attn_params* p, void* cuda_stream);
 
