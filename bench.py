@@ -52,7 +52,7 @@ L2_BYTES = 126 * 1024 * 1024
 # None where no full-size capture exists.
 NCU_TRAFFIC_BYTES = {
     "causal_gqa": 967e6, "softcap_causal": 718e6, "sliding_window": 782e6, "document_causal": 538e6,
-    "evoformer": 190e6, "diff_attn": 407e6,
+    "evoformer": 190e6, "diff_attn": 470e6,
 }
 
 
