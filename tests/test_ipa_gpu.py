@@ -65,3 +65,15 @@ def test_rejects_other_dtypes_and_shapes():
         av.invariant_point_attention(*[a.float() for a in args], None, None, c_hidden=16, no_qk_points=4)
     with pytest.raises(ValueError):
         av.invariant_point_attention(*args, None, None, c_hidden=16, no_qk_points=8)
+
+
+def test_three_dimensional_points_and_other_key_count():
+    """Points with three coordinates (the reference's test stores four), and more keys than queries."""
+    g = torch.Generator(device="cuda").manual_seed(14)
+    r = lambda *s: torch.randn(*s, generator=g, device="cuda").to(torch.bfloat16)
+    B, H, N, Nk, C, Pqk, Pv = 2, 4, 100, 260, 16, 4, 8
+    args = (r(B, H, N, C), r(B, H, Nk, C), r(B, H, Nk, C), r(B, H, N, Pqk, 3), r(B, H, Nk, Pqk, 3), r(B, H, Nk, Pv, 3),
+            r(B, H, N, Nk))
+    out = av.invariant_point_attention(*args, None, None, c_hidden=C, no_qk_points=Pqk)
+    assert out[0].shape == (B, H, N, C) and out[1].shape == (B, N, H, Pv, 3)
+    check(out, ao.invariant_point_attention(*args, c_hidden=C, no_qk_points=Pqk))
